@@ -45,7 +45,7 @@ extern "C" {
 #define VILA_FLAG_STATIC_W 2
 
 const char* vila_last_error(void);
-int vila_abi_version(void); /* 2 */
+int vila_abi_version(void); /* 3 */
 /* Register caller-owned, ZERO-INITIALISED device scratch (256-byte aligned) used by vila_linear's
  * stream-K schedule for fp32 partial sums (64 KiB of counters + M*N*4 bytes per call that uses it;
  * calls that do not fit simply use the data-parallel schedule).  The kernels leave it zeroed again.
@@ -482,8 +482,11 @@ int vila_short_conv_state(const float* h, float* state, const int32_t* seqs, int
 /* Rotary positions + unit norm + cache append for grouped-query attention.  qkv [T, ldq] holds q (H
  * heads of dim) | k (G heads of dim) | v (G heads of vdim).  On the first rot_dims columns of every q
  * and k head the pairs (2i, 2i+1) turn by positions[t] * inv_freq[i] (inv_freq fp64 [rot_dims / 2]);
- * then, if unit_norm, every q and k head is divided by sqrt(mean(head^2) + eps).
- *   q_out fp32 [T, H * dim];  pool row cache_rows[t] = k (G * dim) | v (G * vdim) in pool_dtype. */
+ * then, if unit_norm, every q and k head is divided by sqrt(mean(head^2) + eps) and, where given,
+ * multiplied by q_norm_w / k_norm_w (fp32 [dim], the same for every head).
+ *   q_out fp32 [T, H * dim];  pool row cache_rows[t] = k (G * dim) | v (G * vdim) in pool_dtype.
+ * v_from_k != 0: the row holds q | k only and the values are the keys as they came in (before rotation
+ * and norm); vdim must equal dim. */
 typedef struct vila_rope_append_params {
   const void* qkv;
   int64_t ldq;
@@ -494,6 +497,9 @@ typedef struct vila_rope_append_params {
   void* pool;
   int32_t qkv_dtype, pool_dtype, T, H, G, dim, vdim, rot_dims, unit_norm;
   float eps;
+  const float* q_norm_w; /* [dim] or NULL */
+  const float* k_norm_w; /* [dim] or NULL */
+  int32_t v_from_k;
 } vila_rope_append_params;
 int vila_rope_append(const vila_rope_append_params* p, void* stream);
 
@@ -501,8 +507,11 @@ int vila_rope_append(const vila_rope_append_params* p, void* stream);
  * k (G * dim) | v (G * vdim) per token, fp32 scores / softmax / weighted sum:
  *   s_h(i, j) = scale * <q_h(i), k_{h / (H / G)}(j)>;  if talk: s_h <- sum_g talk[h, g] s_g (all H heads
  *   of a (query, key) pair are mixed before the softmax);  j <= pos(i)
+ *   if dist_bias: s_h += dist_bias[min(pos(i) - j, dist_rows - 1), h]   (after scale and mixing)
+ *   if chunk > 0: only keys with floor(j / chunk) == floor(pos(i) / chunk) are seen (positions count
+ *   from the start of the sequence, whatever the portion)
  *   p_h(i, j) = exp(s_h) / (sum_j exp(s_h) + exp(sink[h]))      (sink == NULL: ordinary softmax)
- *   out_h(i) = sum_j p_h(i, j) v_{h / (H / G)}(j)
+ *   out_h(i) = sum_j p_h(i, j) v_{h / (H / G)}(j);  if gate: out_h(i) *= sigmoid(gate[i, h])
  * tiles [ntiles, 4] = (first batch row, rows (<= 16), position of the first row, slot); page tables as
  * in vila_latent_attention.  nsplit > 1 (tiles of ONE row only: decoded tokens) deals the key blocks of
  * a row to nsplit CTAs; partial is fp32 [T, nsplit, H, vdim + 2], caller-owned. */
@@ -518,6 +527,10 @@ typedef struct vila_paged_attn_params {
   int32_t pool_dtype, out_dtype, ntiles, pt_stride, H, G, dim, vdim, page, nsplit;
   int32_t max_rows; /* largest row count of any tile (1: decoded tokens only) */
   float scale;
+  const float* dist_bias; /* [dist_rows, H] or NULL */
+  const void* gate;       /* [T, ldg] pre-activations, column h = head h, or NULL */
+  int64_t ldg;
+  int32_t dist_rows, chunk, gate_dtype;
 } vila_paged_attn_params;
 int vila_paged_attention(const vila_paged_attn_params* p, void* stream);
 
@@ -565,6 +578,91 @@ int vila_gated_norm_residual_scaled(float* x, const void* part, int part_dtype, 
 int vila_gelu_mul_gather(const void* z, int z_dtype, const void* table, int table_dtype, int64_t ld_table,
                          const int32_t* ids, int col0, void* out, int out_dtype, int rows, int cols,
                          void* stream);
+
+/* ---- State-space mixers on ragged batches: sinusoidal position embedding, causal depthwise
+ * convolution with bias / SiLU, the scalar-decay (state-space duality) and the per-channel selective
+ * recurrences, and the post-normed residual update of two scaled branches. ------------------------- */
+
+/* out[t, c] = table[ids[t], c] * scale + (c odd ? cos : sin)(positions[t] * inv_freq[c / 2])
+ * inv_freq fp64 [(cols + 1) / 2]; the angle is formed in double.  copy (may be NULL) also receives the
+ * rows in copy_dtype. */
+int vila_embed_sincos_rows(const void* table, int table_dtype, const int32_t* ids, const int32_t* positions,
+                           const double* inv_freq, float scale, float* out, void* copy, int copy_dtype,
+                           int rows, int cols, void* stream);
+
+/* x[r, :] += rms(sa * a[r, :] + sb * b[r, :]) * w   with rms(v) = v / sqrt(mean(v^2) + eps); b may be NULL.
+ * copy (may be NULL) receives the updated rows in copy_dtype (the operand of the next projection). */
+int vila_branch_norm_residual(float* x, const void* a, int a_dtype, int64_t lda, float sa, const void* b,
+                              int b_dtype, int64_t ldb, float sb, const void* w, int w_dtype, float eps,
+                              void* copy, int copy_dtype, int rows, int cols, void* stream);
+
+#define VILA_CONV_SILU 1
+/* Causal depthwise convolution over time on `cols` channels of ragged rows:
+ *   out[t, c] = act(bias[c] + sum_{j < taps} w[c, j] * in[t - (taps - 1) + j, c])       (fp32 arithmetic)
+ * Rows before a sequence's portion come from its state slot (fp32 [slots, taps - 1, cols], oldest first),
+ * rows before position 0 are zero.  vila_causal_conv_state stores the last taps - 1 inputs of every
+ * sequence afterwards (same params). */
+typedef struct vila_causal_conv_params {
+  const void* in; /* [rows, ld_in], the channels start at `in` */
+  int64_t ld_in;
+  const void* w;    /* [cols, taps] */
+  const void* bias; /* [cols] or NULL, same dtype as w */
+  float* state;
+  const int32_t* seqs;    /* [nseq, 4] = (first row, rows, first position, slot) */
+  const int32_t* row_seq; /* [rows] */
+  void* out;
+  int64_t ld_out;
+  int32_t in_dtype, w_dtype, out_dtype, rows, nseq, cols, taps, act;
+} vila_causal_conv_params;
+int vila_causal_conv_rows(const vila_causal_conv_params* p, void* stream);
+int vila_causal_conv_state(const vila_causal_conv_params* p, void* stream);
+
+/* vila_ssd_scan — recurrence with one decay per head (state-space duality form), fp32 state:
+ *   dt_t = softplus(dt_raw_t + dt_bias_h),  S_t = exp(-exp(A_log_h) dt_t) S_{t-1} + dt_t B_t x_t^T,
+ *   y_t = S_t^T C_t + D_h x_t,  out_t = y_t * silu(z_t) (z may be NULL)
+ * xbc rows hold x (H heads of P) | B (G groups of N) | C (G groups of N); head h uses group h / (H / G).
+ * state [slots, H, P, N] (N fastest); a sequence at position 0 starts from zero. */
+typedef struct vila_ssd_scan_params {
+  const void* xbc;
+  int64_t ld_xbc;
+  const void* dt; /* [rows, ld_dt], column h */
+  int64_t ld_dt;
+  const void* z; /* [rows, ld_z], H * P columns, or NULL */
+  int64_t ld_z;
+  const float* dt_bias; /* [H] */
+  const float* A_log;   /* [H] */
+  const float* D;       /* [H] */
+  float* state;
+  const int32_t* seqs;
+  void* out; /* [rows, ld_out] */
+  int64_t ld_out;
+  int32_t in_dtype, out_dtype, nseq, H, P, N, G;
+} vila_ssd_scan_params;
+int vila_ssd_scan(const vila_ssd_scan_params* p, void* stream);
+
+/* vila_selective_scan — recurrence with a step size and decay per channel, fp32 state [slots, C, N]:
+ *   dt_t,c = softplus(dt_raw_t,c + dt_bias_c),  S_t[c, n] = exp(-exp(A_log[c, n]) dt_t,c) S_{t-1}[c, n] + dt_t,c x_t,c B_t,n
+ *   y_t,c = sum_n S_t[c, n] C_t,n + D_c x_t,c,  out = y * silu(z) (z may be NULL)
+ * bc rows hold B (N) | C (N). */
+typedef struct vila_selective_scan_params {
+  const void* x; /* [rows, ld_x] */
+  int64_t ld_x;
+  const void* dt; /* [rows, ld_dt] */
+  int64_t ld_dt;
+  const void* bc;
+  int64_t ld_bc;
+  const void* z;
+  int64_t ld_z;
+  const float* dt_bias; /* [C] */
+  const float* A_log;   /* [C, N] */
+  const float* D;       /* [C] */
+  float* state;
+  const int32_t* seqs;
+  void* out;
+  int64_t ld_out;
+  int32_t in_dtype, out_dtype, nseq, C, N;
+} vila_selective_scan_params;
+int vila_selective_scan(const vila_selective_scan_params* p, void* stream);
 
 #ifdef __cplusplus
 }

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     # and every ctypes signature corresponds to a declared function
     for n in _lib.SIGNATURES:
         assert n in names, f"{n} bound in _lib.py but not declared in the header"
-    assert lib.vila_abi_version() == 2
+    assert lib.vila_abi_version() == 3
 
 
 def test_struct_layouts_match_header_field_order():
@@ -39,7 +39,11 @@ def test_struct_layouts_match_header_field_order():
                        ("vila_glinear_params", _lib.GLinearParams),
                        ("vila_latent_attn_params", _lib.LatentAttnParams),
                        ("vila_hgrn2_params", _lib.Hgrn2Params),
-                       ("vila_sink_attn_params", _lib.SinkAttnParams)):
+                       ("vila_sink_attn_params", _lib.SinkAttnParams),
+                       ("vila_rope_append_params", _lib.RopeAppendParams),
+                       ("vila_paged_attn_params", _lib.PagedAttnParams),
+                       ("vila_ssd_scan_params", _lib.SsdScanParams),
+                       ("vila_selective_scan_params", _lib.SelectiveScanParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []

@@ -122,6 +122,7 @@ class RopeAppendParams(C.Structure):
         ("qkv_dtype", C.c_int32), ("pool_dtype", C.c_int32), ("T", C.c_int32), ("H", C.c_int32),
         ("G", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("rot_dims", C.c_int32),
         ("unit_norm", C.c_int32), ("eps", c_float),
+        ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("v_from_k", C.c_int32),
     ]
 
 
@@ -132,6 +133,36 @@ class PagedAttnParams(C.Structure):
         ("pool_dtype", C.c_int32), ("out_dtype", C.c_int32), ("ntiles", C.c_int32), ("pt_stride", C.c_int32),
         ("H", C.c_int32), ("G", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("page", C.c_int32),
         ("nsplit", C.c_int32), ("max_rows", C.c_int32), ("scale", c_float),
+        ("dist_bias", c_void_p), ("gate", c_void_p), ("ldg", c_i64),
+        ("dist_rows", C.c_int32), ("chunk", C.c_int32), ("gate_dtype", C.c_int32),
+    ]
+
+
+class CausalConvParams(C.Structure):
+    _fields_ = [
+        ("in_", c_void_p), ("ld_in", c_i64), ("w", c_void_p), ("bias", c_void_p), ("state", c_void_p),
+        ("seqs", c_void_p), ("row_seq", c_void_p), ("out", c_void_p), ("ld_out", c_i64),
+        ("in_dtype", C.c_int32), ("w_dtype", C.c_int32), ("out_dtype", C.c_int32), ("rows", C.c_int32),
+        ("nseq", C.c_int32), ("cols", C.c_int32), ("taps", C.c_int32), ("act", C.c_int32),
+    ]
+
+
+class SsdScanParams(C.Structure):
+    _fields_ = [
+        ("xbc", c_void_p), ("ld_xbc", c_i64), ("dt", c_void_p), ("ld_dt", c_i64), ("z", c_void_p), ("ld_z", c_i64),
+        ("dt_bias", c_void_p), ("A_log", c_void_p), ("D", c_void_p), ("state", c_void_p), ("seqs", c_void_p),
+        ("out", c_void_p), ("ld_out", c_i64),
+        ("in_dtype", C.c_int32), ("out_dtype", C.c_int32), ("nseq", C.c_int32), ("H", C.c_int32),
+        ("P", C.c_int32), ("N", C.c_int32), ("G", C.c_int32),
+    ]
+
+
+class SelectiveScanParams(C.Structure):
+    _fields_ = [
+        ("x", c_void_p), ("ld_x", c_i64), ("dt", c_void_p), ("ld_dt", c_i64), ("bc", c_void_p), ("ld_bc", c_i64),
+        ("z", c_void_p), ("ld_z", c_i64), ("dt_bias", c_void_p), ("A_log", c_void_p), ("D", c_void_p),
+        ("state", c_void_p), ("seqs", c_void_p), ("out", c_void_p), ("ld_out", c_i64),
+        ("in_dtype", C.c_int32), ("out_dtype", C.c_int32), ("nseq", C.c_int32), ("C", C.c_int32), ("N", C.c_int32),
     ]
 
 
@@ -215,6 +246,14 @@ SIGNATURES = {
                                         c_int, c_void_p, c_int, c_float, c_float, c_float, c_int, c_int, c_void_p],
     "vila_gelu_mul_gather": [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                              c_void_p],
+    "vila_embed_sincos_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                               c_int, c_int, c_void_p],
+    "vila_branch_norm_residual": [c_void_p, c_void_p, c_int, c_i64, c_float, c_void_p, c_int, c_i64, c_float,
+                                  c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "vila_causal_conv_rows": [C.POINTER(CausalConvParams), c_void_p],
+    "vila_causal_conv_state": [C.POINTER(CausalConvParams), c_void_p],
+    "vila_ssd_scan": [C.POINTER(SsdScanParams), c_void_p],
+    "vila_selective_scan": [C.POINTER(SelectiveScanParams), c_void_p],
 }
 _RESTYPES = {"vila_last_error": C.c_char_p}
 

@@ -36,6 +36,7 @@ SOURCES = [
     "hgrn2.cu",
     "short_conv.cu",
     "paged_attn.cu",
+    "ssm.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h", "dtype_any.cuh", "../../include/vila_b200.h"]
 

@@ -42,7 +42,7 @@ static int require_sm100() {
 extern "C" {
 
 const char* vila_last_error(void) { return vb::last_error(); }
-int vila_abi_version(void) { return 2; }
+int vila_abi_version(void) { return 3; }
 
 int vila_set_workspace(void* ptr, uint64_t bytes) { return vb::set_workspace(ptr, (size_t)bytes); }
 
@@ -472,6 +472,42 @@ int vila_gelu_mul_gather(const void* z, int z_dtype, const void* table, int tabl
                          void* stream) {
   VB_REQUIRE_DEVICE();
   return vb::gelu_mul_gather(z, z_dtype, table, table_dtype, ld_table, ids, col0, out, out_dtype, rows, cols, st(stream));
+}
+
+int vila_embed_sincos_rows(const void* table, int table_dtype, const int32_t* ids, const int32_t* positions,
+                           const double* inv_freq, float scale, float* out, void* copy, int copy_dtype,
+                           int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::embed_sincos_rows(table, table_dtype, ids, positions, inv_freq, scale, out, copy, copy_dtype, rows,
+                               cols, st(stream));
+}
+
+int vila_branch_norm_residual(float* x, const void* a, int a_dtype, int64_t lda, float sa, const void* b,
+                              int b_dtype, int64_t ldb, float sb, const void* w, int w_dtype, float eps,
+                              void* copy, int copy_dtype, int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::branch_norm_residual(x, a, a_dtype, lda, sa, b, b_dtype, ldb, sb, w, w_dtype, eps, copy, copy_dtype,
+                                  rows, cols, st(stream));
+}
+
+int vila_causal_conv_rows(const vila_causal_conv_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::causal_conv_rows(*p, st(stream));
+}
+
+int vila_causal_conv_state(const vila_causal_conv_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::causal_conv_state(*p, st(stream));
+}
+
+int vila_ssd_scan(const vila_ssd_scan_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::ssd_scan(*p, st(stream));
+}
+
+int vila_selective_scan(const vila_selective_scan_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::selective_scan(*p, st(stream));
 }
 
 }  // extern "C"

@@ -457,8 +457,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float xb = bf16_round(v[j] + bias);
-            const float y = act == ACT_GELU_TANH ? gelu_tanh_f(xb)
-                                                 : (act == ACT_GELU_ERF ? gelu_erf_f(xb) : silu_f(xb));
+            const float y = act == ACT_GELU_TANH
+                                ? gelu_tanh_f(xb)
+                                : (act == ACT_GELU_ERF ? gelu_erf_f(xb)
+                                                       : (act == ACT_RELU2 ? fmaxf(xb, 0.f) * fmaxf(xb, 0.f) : silu_f(xb)));
             sts_bf16(dst + j * kStgPitch, y);
           }
         }

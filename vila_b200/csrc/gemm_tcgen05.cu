@@ -466,7 +466,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               float x = bf16_round(v[j]);
               v[j] = epi.act == ACT_GELU_TANH
                          ? gelu_tanh_f(x)
-                         : (epi.act == ACT_GELU_ERF ? gelu_erf_f(x) : silu_f(x));
+                         : (epi.act == ACT_GELU_ERF ? gelu_erf_f(x)
+                                                    : (epi.act == ACT_RELU2 ? fmaxf(x, 0.f) * fmaxf(x, 0.f) : silu_f(x)));
             }
           }
           if (row_ok) {

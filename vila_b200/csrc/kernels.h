@@ -7,7 +7,7 @@
 
 namespace vb {
 
-enum Act : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2, ACT_SILU = 3 };
+enum Act : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2, ACT_SILU = 3, ACT_RELU2 = 4 };
 
 struct GemmEpilogue {
   const __nv_bfloat16* bias = nullptr;      // [N]
@@ -252,6 +252,11 @@ int moe_route(const void* x, int x_dt, int64_t ldx, const float* wr, const float
               float* weight, int rows, int cols, int experts, int top, cudaStream_t stream);
 int moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
               cudaStream_t stream);
+int embed_sincos_rows(const void* table, int dt, const int32_t* ids, const int32_t* positions, const double* inv_freq,
+                      float scale, float* out, void* copy, int c_dt, int rows, int cols, cudaStream_t stream);
+int branch_norm_residual(float* x, const void* a, int a_dt, int64_t lda, float sa, const void* b, int b_dt,
+                         int64_t ldb, float sb, const void* w, int w_dt, float eps, void* copy, int c_dt, int rows,
+                         int cols, cudaStream_t stream);
 }  // namespace vb
 struct vila_glinear_params;
 struct vila_latent_attn_params;
@@ -261,7 +266,14 @@ struct vila_glinear_ext;
 struct vila_rope_append_params;
 struct vila_paged_attn_params;
 struct vila_norm_conv_params;
+struct vila_causal_conv_params;
+struct vila_ssd_scan_params;
+struct vila_selective_scan_params;
 namespace vb {
+int causal_conv_rows(const vila_causal_conv_params& p, cudaStream_t stream);
+int causal_conv_state(const vila_causal_conv_params& p, cudaStream_t stream);
+int ssd_scan(const vila_ssd_scan_params& p, cudaStream_t stream);
+int selective_scan(const vila_selective_scan_params& p, cudaStream_t stream);
 int norm_conv_rows(const vila_norm_conv_params& p, cudaStream_t stream);
 int rope_append(const vila_rope_append_params& p, cudaStream_t stream);
 int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream);

@@ -11,6 +11,10 @@
 //                        prompt portions use BQ up to 16, decoded tokens BQ = 1 with the key blocks of a
 //                        row dealt to nsplit CTAs
 //   paged_attn_merge_kernel  merges the nsplit partial (max, sum, weighted sum) triples of a decoded token
+// Options another architecture can combine freely: an additive bias looked up by the distance between
+// query and key (dist_bias [dist_rows, H], the last row serves every larger distance; added after scale and
+// mixing), a chunked mask (a query sees the keys of its own block of `chunk` positions only; the key loop
+// starts at the block of the tile's first row), and a per-(token, head) sigmoid gate on the output.
 // Every reduction over keys runs in key order inside a block and block by block, so a row's result does
 // not depend on what else is in the launch.
 #include "../../include/vila_b200.h"
@@ -63,18 +67,23 @@ __global__ void __launch_bounds__(kThreads) rope_append_kernel(const vila_rope_a
     }
     ss = warp_sum(ss);
     const float r = p.unit_norm ? 1.0f / sqrtf(ss / static_cast<float>(p.dim) + p.eps) : 1.0f;
+    const float* nw = is_q ? p.q_norm_w : p.k_norm_w;
     for (int c = lane; c < p.dim; c += 32) {
       float v = ld_any(p.qkv, p.qkv_dtype, src + c);
+      if (p.v_from_k && !is_q)   // the value is the key as it came in
+        st_any(p.pool, p.pool_dtype, prow + static_cast<size_t>(p.G) * p.dim + static_cast<size_t>(hh - p.H) * p.dim + c, v);
       if (c < p.rot_dims) {
         const float o = ld_any(p.qkv, p.qkv_dtype, src + (c ^ 1));
         const float co = cs[c >> 1], si = cs[half + (c >> 1)];
         v = (c & 1) ? fmaf(v, co, o * si) : fmaf(v, co, -(o * si));
       }
       v *= r;
+      if (nw) v *= nw[c];
       if (is_q) p.q_out[(static_cast<size_t>(t) * p.H + hh) * p.dim + c] = v;
       else st_any(p.pool, p.pool_dtype, prow + static_cast<size_t>(hh - p.H) * p.dim + c, v);
     }
   }
+  if (p.v_from_k) return;
   const size_t vsrc = in0 + static_cast<size_t>(p.H + p.G) * p.dim, vdst = prow + static_cast<size_t>(p.G) * p.dim;
   for (int c = tid; c < p.G * p.vdim; c += kThreads)
     st_any(p.pool, p.pool_dtype, vdst + c, ld_any(p.qkv, p.qkv_dtype, vsrc + c));
@@ -89,6 +98,17 @@ struct AttnShape {
 
 __device__ __forceinline__ size_t pool_row(const int32_t* pt, int page, int j) {
   return static_cast<size_t>(pt[j / page]) * page + (j % page);
+}
+
+// first key a query at position pos can see
+__device__ __forceinline__ int first_key(const vila_paged_attn_params& p, int pos) {
+  return p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0;
+}
+__device__ __forceinline__ float dist_bias(const vila_paged_attn_params& p, int dist, int h) {
+  return __ldg(p.dist_bias + static_cast<size_t>(min(dist, p.dist_rows - 1)) * p.H + h);
+}
+__device__ __forceinline__ float out_gate(const vila_paged_attn_params& p, int row, int h) {
+  return p.gate ? sigmoid_f(ld_any(p.gate, p.gate_dtype, static_cast<size_t>(row) * p.ldg + h)) : 1.0f;
 }
 
 // K | V rows of a key block, widened to fp32: one warp per key.  16-byte loads when the head sizes allow
@@ -199,8 +219,9 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
   const int nout = R * vq;                // float4 accumulators of the CTA: index o -> (r, c4)
   const int nkeys = pos0 + n;             // keys 0 .. nkeys - 1 are visible to the last row
   const int nblocks = (nkeys + BK - 1) / BK;
+  const int b0 = first_key(p, pos0) / BK;   // the first row's chunk starts first
 
-  for (int b = split; b < nblocks; b += nsplit) {
+  for (int b = b0 + split; b < nblocks; b += nsplit) {
     const int j0 = b * BK;
     __syncthreads();
     load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4);
@@ -222,13 +243,14 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
     // head mixing + mask + online softmax: a warp per score row, a lane per key
     for (int r = warp; r < R; r += kWarps) {
       const int i = r / H, h = r - i * H;
-      const bool valid = lane < BK && i < n && j0 + lane <= pos0 + i;
+      const bool valid = lane < BK && i < n && j0 + lane <= pos0 + i && j0 + lane >= first_key(p, pos0 + i);
       float s = 0.f;
       if (lane < BK) {
         const float* tk = Tk + h * H;
         const float* sr = Ss + (i * H) * BK + lane;
         for (int g = 0; g < H; ++g) s = fmaf(tk[g], sr[g * BK], s);
       }
+      if (valid && p.dist_bias) s += dist_bias(p, pos0 + i - (j0 + lane), h);
       s = valid ? s : kNegBig;
       const float m_old = m_s[r];
       const float m_new = fmaxf(m_old, warp_max(s));
@@ -272,7 +294,7 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
     if (i >= n) continue;
     const float v[4] = {acc[a].x, acc[a].y, acc[a].z, acc[a].w};
     if (nsplit == 1) {
-      const float inv = 1.0f / l_s[r];
+      const float inv = out_gate(p, row0 + i, h) / l_s[r];
       const size_t ob = (static_cast<size_t>(row0 + i) * H + h) * V + 4 * c4;
 #pragma unroll
       for (int e = 0; e < 4; ++e)
@@ -337,7 +359,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
   const int nkeys = pos0 + n;
   const int d4n = D4 >> 2;
 
-  for (int j0 = 0; j0 < nkeys; j0 += BK) {
+  for (int j0 = (first_key(p, pos0) / BK) * BK; j0 < nkeys; j0 += BK) {
     __syncthreads();
     load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, NT / 32);
     __syncthreads();
@@ -382,7 +404,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
         mo[u] = kNegBig;
         if (r < R) {
           const int h = r / BQ, i = r - h * BQ;
-          ok[u] = lane < BK && i < n && j0 + lane <= pos0 + i;
+          ok[u] = lane < BK && i < n && j0 + lane <= pos0 + i && j0 + lane >= first_key(p, pos0 + i);
           if (lane < BK) {
             const float* tk = Tk + h * H;
             const float* sr = Ss + i * BK + lane;
@@ -393,7 +415,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
               s1 = fmaf(tk[g + 1], sr[(g + 1) * BQ * BK], s1);
             }
             if (g < H) s0 = fmaf(tk[g], sr[g * BQ * BK], s0);
-            if (ok[u]) sv[u] = s0 + s1;
+            if (ok[u]) sv[u] = s0 + s1 + (p.dist_bias ? dist_bias(p, pos0 + i - (j0 + lane), h) : 0.f);
           }
           mo[u] = m_s[r];
         }
@@ -467,7 +489,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
     for (int k = 0; k < 4; ++k) {
       const int r = (rb << 2) + k, h = r / BQ, i = r - h * BQ;
       if (i >= n) continue;
-      const float inv = 1.0f / l_s[r];
+      const float inv = out_gate(p, row0 + i, h) / l_s[r];
       const float v[4] = {acc[a][k].x, acc[a][k].y, acc[a][k].z, acc[a][k].w};
       const size_t ob = (static_cast<size_t>(row0 + i) * H + h) * V + 4 * c4;
 #pragma unroll
@@ -487,7 +509,7 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const vila_paged_
   for (int s = 0; s < ns; ++s) mx = fmaxf(mx, part[s * stride + V]);
   float den = 0.f;
   for (int s = 0; s < ns; ++s) den += expf(part[s * stride + V] - mx) * part[s * stride + V + 1];
-  const float inv = 1.0f / den;
+  const float inv = out_gate(p, row, h) / den;
   for (int k = threadIdx.x; k < V; k += blockDim.x) {
     float a = 0.f;
     for (int s = 0; s < ns; ++s) a += expf(part[s * stride + V] - mx) * part[s * stride + k];
@@ -506,8 +528,9 @@ size_t attn_smem(const vila_paged_attn_params& p, int BQ, int BK) {
 int rope_append(const vila_rope_append_params& p, cudaStream_t stream) {
   if (p.T <= 0) return 0;
   VB_CHECK(p.H >= 1 && p.G >= 1 && p.dim >= 1 && p.vdim >= 1 && p.rot_dims >= 0 && p.rot_dims <= p.dim &&
-               p.rot_dims % 2 == 0 && (p.rot_dims == 0 || p.inv_freq != nullptr),
-           "rope_append: H=%d G=%d dim=%d vdim=%d rot_dims=%d", p.H, p.G, p.dim, p.vdim, p.rot_dims);
+               p.rot_dims % 2 == 0 && (p.rot_dims == 0 || p.inv_freq != nullptr) && (!p.v_from_k || p.vdim == p.dim),
+           "rope_append: H=%d G=%d dim=%d vdim=%d rot_dims=%d v_from_k=%d", p.H, p.G, p.dim, p.vdim, p.rot_dims,
+           p.v_from_k);
   VB_CUDA(launch_serial(rope_append_kernel, dim3(p.T), dim3(kThreads), sizeof(float) * (p.rot_dims + 2), stream, p));
   return 0;
 }
@@ -518,6 +541,8 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
                p.nsplit <= 64 && (p.nsplit == 1 || p.partial != nullptr),
            "paged_attention: H=%d G=%d dim=%d vdim=%d page=%d nsplit=%d", p.H, p.G, p.dim, p.vdim, p.page, p.nsplit);
   constexpr size_t kSmemMax = 224 * 1024;
+  VB_CHECK(p.chunk >= 0 && (p.dist_bias == nullptr || p.dist_rows >= 1), "paged_attention: chunk=%d dist_rows=%d",
+           p.chunk, p.dist_rows);
   VB_CHECK(p.max_rows >= 1 && p.max_rows <= 16 && (p.nsplit == 1 || p.max_rows == 1),
            "paged_attention: max_rows=%d nsplit=%d (key splitting serves one-row tiles)", p.max_rows, p.nsplit);
   AttnShape sh;

@@ -354,6 +354,62 @@ inline int flat_grid(size_t total) {
   return static_cast<int>(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
 }
 
+// ---- scaled embedding + sinusoidal positions ---------------------------------------------------------
+// A warp per row; a lane takes column pairs (2i, 2i + 1) = (sin, cos) of ONE angle position * inv_freq[i],
+// formed and evaluated in double so that far positions keep their phase.
+__global__ void __launch_bounds__(kRowThreads)
+embed_sincos_rows_kernel(const void* __restrict__ table, int dt, const int32_t* __restrict__ ids,
+                         const int32_t* __restrict__ positions, const double* __restrict__ inv_freq, float scale,
+                         float* __restrict__ out, void* __restrict__ copy, int c_dt, int rows, int cols) {
+  const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t src = static_cast<size_t>(ids[row]) * cols, dst = static_cast<size_t>(row) * cols;
+  const double pos = static_cast<double>(positions[row]);
+  for (int i = lane_id(); 2 * i < cols; i += 32) {
+    double sn, cs;
+    sincos(pos * inv_freq[i], &sn, &cs);
+    const float v0 = fmaf(ld_any(table, dt, src + 2 * i), scale, static_cast<float>(sn));
+    out[dst + 2 * i] = v0;
+    if (copy) st_any(copy, c_dt, dst + 2 * i, v0);
+    if (2 * i + 1 < cols) {
+      const float v1 = fmaf(ld_any(table, dt, src + 2 * i + 1), scale, static_cast<float>(cs));
+      out[dst + 2 * i + 1] = v1;
+      if (copy) st_any(copy, c_dt, dst + 2 * i + 1, v1);
+    }
+  }
+}
+
+// ---- post-normed residual update of one or two scaled branches ---------------------------------------
+// x += rms(sa * a + sb * b) * w  (the norm sits on the sublayer's OUTPUT); optionally the updated row is
+// also written in the dtype of the next projection's operand.
+template <int TPR>
+__global__ void __launch_bounds__(kRowThreads)
+branch_norm_residual_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dt, int64_t lda, float sa,
+                            const void* __restrict__ b, int b_dt, int64_t ldb, float sb,
+                            const void* __restrict__ w, int w_dt, float eps, void* __restrict__ copy, int c_dt,
+                            int rows, int cols) {
+  __shared__ float red[kRowsPerCta];
+  const int row = row_of<TPR>();
+  if (row >= rows) return;
+  const size_t ab = static_cast<size_t>(row) * lda, bb = static_cast<size_t>(row) * ldb;
+  float ss = 0.f;
+  for (int c = col0_of<TPR>(); c < cols; c += TPR) {
+    float y = sa * ld_any(a, a_dt, ab + c);
+    if (b) y = fmaf(sb, ld_any(b, b_dt, bb + c), y);
+    ss = fmaf(y, y, ss);
+  }
+  ss = row_sum<TPR>(ss, red);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+  const size_t xb = static_cast<size_t>(row) * cols;
+  for (int c = col0_of<TPR>(); c < cols; c += TPR) {
+    float y = sa * ld_any(a, a_dt, ab + c);
+    if (b) y = fmaf(sb, ld_any(b, b_dt, bb + c), y);
+    const float v = x[xb + c] + y * r * (w ? ld_any(w, w_dt, c) : 1.0f);
+    x[xb + c] = v;
+    if (copy) st_any(copy, c_dt, xb + c, v);
+  }
+}
+
 }  // namespace
 
 int embed_rows(const void* table, int dt, const int32_t* ids, float* out, int rows, int cols,
@@ -467,6 +523,29 @@ int moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int 
   VB_CHECK(experts >= 1 && experts <= 8192 && pairs >= 0, "moe_group: experts=%d pairs=%d", experts, pairs);
   VB_CUDA(launch_serial(moe_group_kernel, dim3(1), dim3(1024), sizeof(int) * (experts + 1), stream, idx, seg,
                      sorted, pairs, experts));
+  return 0;
+}
+
+int embed_sincos_rows(const void* table, int dt, const int32_t* ids, const int32_t* positions, const double* inv_freq,
+                      float scale, float* out, void* copy, int c_dt, int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  VB_CHECK(cols >= 1 && inv_freq != nullptr && positions != nullptr, "embed_sincos_rows: cols=%d", cols);
+  VB_CUDA(launch_serial(embed_sincos_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, table, dt, ids,
+                        positions, inv_freq, scale, out, copy, c_dt, rows, cols));
+  return 0;
+}
+
+int branch_norm_residual(float* x, const void* a, int a_dt, int64_t lda, float sa, const void* b, int b_dt,
+                         int64_t ldb, float sb, const void* w, int w_dt, float eps, void* copy, int c_dt, int rows,
+                         int cols, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  VB_CHECK(cols > 0 && a != nullptr, "branch_norm_residual: cols=%d", cols);
+  if (cols >= kWideCols)
+    VB_CUDA(launch_serial(branch_norm_residual_kernel<256>, dim3(rows), dim3(kRowThreads), 0, stream, x, a, a_dt, lda,
+                          sa, b, b_dt, ldb, sb, w, w_dt, eps, copy, c_dt, rows, cols));
+  else
+    VB_CUDA(launch_serial(branch_norm_residual_kernel<32>, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x, a,
+                          a_dt, lda, sa, b, b_dt, ldb, sb, w, w_dt, eps, copy, c_dt, rows, cols));
   return 0;
 }
 

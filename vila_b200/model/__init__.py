@@ -6,6 +6,7 @@ from .llava_llama import (BasicImageEncoder, BasicVideoEncoder, LlavaLlamaModel,
 from .lufatar import LufatarConfig, LufatarForCausalLM, LufatarLayerConfig
 from .modeling_vila import VILAForCausalLM
 from .moronex import MoronexConfig, MoronexForCausalLM, MoronexLayerConfig
+from .nusovik import NusovikConfig, NusovikForCausalLM, NusovikLayerConfig
 from .projector import MultimodalProjector
 from .registry import LANGUAGE_MODELS, language_model_architecture, load_language_model
 from .qwen2 import GraphDecoder, MegaDecoder, PagedKVCache, Qwen2ForCausalLM

@@ -10,8 +10,10 @@ import torch
 
 from .lufatar import LufatarForCausalLM
 from .moronex import MoronexForCausalLM
+from .nusovik import NusovikForCausalLM
 
-LANGUAGE_MODELS: Dict[str, type] = {"Moronex": MoronexForCausalLM, "Lufatar": LufatarForCausalLM}
+LANGUAGE_MODELS: Dict[str, type] = {"Moronex": MoronexForCausalLM, "Lufatar": LufatarForCausalLM,
+                                    "Nusovik": NusovikForCausalLM}
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 

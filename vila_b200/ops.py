@@ -626,15 +626,16 @@ def sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tiles: tor
 
 
 # ---- parallel-sublayer decoders: pair embedding, short convolution, rotary GQA over a paged pool, sigmoid router ----
-def linear_any(x: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out_dtype=None) -> torch.Tensor:
-    """x [M, K] · w[N, K]^T: bf16 operands with 16-byte aligned rows go to the tcgen05 GEMM, everything
-    else (fp32 tensors, odd shapes, an fp32 result) to the CUDA-core grouped kernel."""
+def linear_any(x: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out_dtype=None,
+               bias: Optional[torch.Tensor] = None, act: int = ACT_NONE) -> torch.Tensor:
+    """act(x [M, K] · w[N, K]^T + bias): bf16 operands with 16-byte aligned rows go to the tcgen05 GEMM,
+    everything else (fp32 tensors, odd shapes, an fp32 result) to the CUDA-core grouped kernel."""
     N, K = w.shape
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16)
             and K % 8 == 0 and N % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and (not swiglu or N % 32 == 0)):
-        return linear(x, w, swiglu=swiglu, static_w=True)
-    return glinear(x, w, swiglu=swiglu, out_dtype=out_dtype)
+        return linear(x, w, bias, act=act, swiglu=swiglu, static_w=True)
+    return glinear(x, w, swiglu=swiglu, out_dtype=out_dtype, bias=bias, act=act)
 
 
 def embed_pair_rows(table: torch.Tensor, pair_table: torch.Tensor, ids: torch.Tensor, prev_ids: torch.Tensor,
@@ -711,11 +712,15 @@ def norm_conv_rows(x: torch.Tensor, norm_w: Sequence[torch.Tensor], conv_w: Sequ
 
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Tensor, pool: torch.Tensor, *,
                 heads: int, kv_heads: int, dim: int, vdim: int, inv_freq: Optional[torch.Tensor],
-                unit_norm: bool, eps: float) -> torch.Tensor:
+                unit_norm: bool, eps: float, q_norm_w: Optional[torch.Tensor] = None,
+                k_norm_w: Optional[torch.Tensor] = None, v_from_k: bool = False) -> torch.Tensor:
     """qkv [T, >= heads*dim + kv_heads*(dim+vdim)] -> q fp32 [T, heads*dim] (rotated, unit-normed); the
     token's k | v go to row cache_rows[t] of pool [pool rows, kv_heads*(dim+vdim)].  inv_freq float64
-    [rot_dims / 2] (None: no rotation)."""
-    assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= heads * dim + kv_heads * (dim + vdim)
+    [rot_dims / 2] (None: no rotation).  q_norm_w / k_norm_w fp32 [dim]: weights of the per-head norm.
+    v_from_k: qkv holds q | k only, the cached value of a token is its incoming key (before rotation / norm)."""
+    assert qkv.dim() == 2 and qkv.stride(1) == 1
+    assert qkv.shape[1] >= heads * dim + kv_heads * (dim if v_from_k else dim + vdim)
+    assert not v_from_k or vdim == dim
     assert pool.dim() == 2 and pool.is_contiguous() and pool.shape[1] == kv_heads * (dim + vdim)
     T = qkv.shape[0]
     q = torch.empty(T, heads * dim, dtype=torch.float32, device=qkv.device)
@@ -730,6 +735,9 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Te
     p.T, p.H, p.G, p.dim, p.vdim = T, heads, kv_heads, dim, vdim
     p.rot_dims = 0 if inv_freq is None else 2 * inv_freq.numel()
     p.unit_norm, p.eps = 1 if unit_norm else 0, eps
+    for t_ in (q_norm_w, k_norm_w):
+        assert t_ is None or (unit_norm and t_.numel() == dim)
+    p.q_norm_w, p.k_norm_w, p.v_from_k = _f32(q_norm_w, "q_norm_w"), _f32(k_norm_w, "k_norm_w"), 1 if v_from_k else 0
     check(_lib.load().vila_rope_append(C.byref(p), _stream()), "vila_rope_append")
     return q
 
@@ -738,11 +746,15 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, page_tables: torch.Tens
                     heads: int, kv_heads: int, dim: int, vdim: int, page: int, scale: float,
                     talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
                     out: Optional[torch.Tensor] = None, out_dtype=None, max_rows: int = 16,
-                    nsplit: int = 1) -> torch.Tensor:
+                    nsplit: int = 1, dist_bias: Optional[torch.Tensor] = None, chunk: int = 0,
+                    gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal grouped-query attention of q fp32 [T, heads*dim] over the paged k | v pool, fp32 scores and
     softmax, optional mixing of the heads' scores (talk fp32 [heads, heads]) and per-head sink logit in
     the denominator.  tiles int32 [n, 4] = (row0, rows <= max_rows, pos0, slot) -> [T, heads*vdim].
-    nsplit > 1 (one-row tiles only) spreads the keys of a row over nsplit CTAs + a merge kernel."""
+    nsplit > 1 (one-row tiles only) spreads the keys of a row over nsplit CTAs + a merge kernel.
+    dist_bias fp32 [rows, heads]: added to the score by distance (the last row for every larger one);
+    chunk > 0: a query sees its own block of `chunk` positions only; gate [T, >= heads] (a view with a
+    row stride is fine): the output of head h is multiplied by sigmoid(gate[t, h])."""
     assert q.dtype == torch.float32 and q.is_contiguous() and q.shape[1] == heads * dim
     assert pool.dim() == 2 and pool.is_contiguous() and pool.shape[1] == kv_heads * (dim + vdim)
     if out is None:
@@ -758,6 +770,13 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, page_tables: torch.Tens
     p.ntiles, p.pt_stride = tiles.shape[0], page_tables.stride(0)
     p.H, p.G, p.dim, p.vdim, p.page, p.scale = heads, kv_heads, dim, vdim, page, scale
     p.max_rows = max_rows
+    if dist_bias is not None:
+        assert dist_bias.dim() == 2 and dist_bias.shape[1] == heads
+        p.dist_bias, p.dist_rows = _f32(dist_bias, "dist_bias"), dist_bias.shape[0]
+    if gate is not None:
+        assert gate.dim() == 2 and gate.shape[0] == q.shape[0] and gate.shape[1] >= heads and gate.stride(1) == 1
+        p.gate, p.ldg, p.gate_dtype = _p(gate), gate.stride(0), _dt(gate, "gate")
+    p.chunk = int(chunk)
     p.nsplit = max(1, int(nsplit)) if max_rows == 1 else 1
     partial = None
     if p.nsplit > 1:
@@ -810,4 +829,125 @@ def gelu_mul_gather(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col
     check(_lib.load().vila_gelu_mul_gather(_p(z), _dt(z, "z"), _p(table), _dt(table, "table"), table.stride(0), _i32(ids, "ids"),
                                            col0, _p(out), _dt(out, "out"), z.shape[0], z.shape[1], _stream()),
           "vila_gelu_mul_gather")
+    return out
+
+
+# ---- state-space mixers: sinusoidal embedding, causal convolution, scalar-decay and selective scans ----
+def embed_sincos_rows(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                      scale: float, *, copy_dtype=None):
+    """fp32 rows table[ids] * scale + sinusoid(positions): column 2i = sin, 2i + 1 = cos of position *
+    inv_freq[i] (float64 [(cols + 1) // 2]).  -> (rows, the same rows in copy_dtype or None)"""
+    T, cols = ids.numel(), table.shape[1]
+    assert table.is_contiguous() and inv_freq.dtype == torch.float64 and inv_freq.is_cuda and \
+        inv_freq.is_contiguous() and inv_freq.numel() == (cols + 1) // 2
+    out = torch.empty(T, cols, dtype=torch.float32, device=table.device)
+    copy = torch.empty(T, cols, dtype=copy_dtype, device=table.device) if copy_dtype is not None else None
+    check(_lib.load().vila_embed_sincos_rows(_p(table), _dt(table, "table"), _i32(ids, "ids"),
+                                             _i32(positions, "positions"), _p(inv_freq), scale, _p(out), _p(copy),
+                                             _dt(copy, "copy") if copy is not None else 0, T, cols, _stream()),
+          "vila_embed_sincos_rows")
+    return out, copy
+
+
+def branch_norm_residual(x: torch.Tensor, a: torch.Tensor, w: Optional[torch.Tensor], eps: float, *,
+                         a_scale: float = 1.0, b: Optional[torch.Tensor] = None, b_scale: float = 1.0,
+                         copy_dtype=None) -> Optional[torch.Tensor]:
+    """x fp32 [rows, cols] (in place) += rms(a_scale * a + b_scale * b) * w, rms(v) = v / sqrt(mean(v^2) + eps):
+    the post-normed residual update of one or two branches.  copy_dtype: also return the updated rows in
+    that dtype (the operand of the projection that reads x next)."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    rows, cols = x.shape
+    assert a.shape == (rows, cols) and a.stride(1) == 1
+    if b is not None:
+        assert b.shape == (rows, cols) and b.stride(1) == 1
+    copy = torch.empty(rows, cols, dtype=copy_dtype, device=x.device) if copy_dtype is not None else None
+    check(_lib.load().vila_branch_norm_residual(
+        _p(x), _p(a), _dt(a, "a"), a.stride(0), a_scale, _p(b), _dt(b, "b") if b is not None else 0,
+        b.stride(0) if b is not None else 0, b_scale, _p(w), _dt(w, "w") if w is not None else 0, eps,
+        _p(copy), _dt(copy, "copy") if copy is not None else 0, rows, cols, _stream()), "vila_branch_norm_residual")
+    return copy
+
+
+CONV_NONE, CONV_SILU = 0, 1
+
+
+def causal_conv_rows(u: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                     seqs: torch.Tensor, row_seq: torch.Tensor, *, act: int = CONV_NONE, out_dtype=None,
+                     update_state: bool = True) -> torch.Tensor:
+    """u [T, C] (a column slice with a row stride is fine) -> act(bias + causal depthwise convolution over time
+    with w [C, taps]; tap taps - 1 meets the newest input); state fp32 [slots, taps - 1, C] holds every sequence's
+    last taps - 1 inputs (read for taps that reach before the portion, then replaced by this portion's last
+    inputs); seqs int32 [n, 4] = (row0, rows, pos0, slot), row_seq int32 [T]."""
+    assert u.dim() == 2 and u.stride(1) == 1
+    T, Cc = u.shape
+    taps = w.shape[1]
+    assert w.shape == (Cc, taps) and w.is_contiguous()
+    if bias is not None:
+        assert bias.dtype == w.dtype and bias.numel() == Cc and bias.is_contiguous()
+    if taps > 1:
+        assert state is not None and state.dtype == torch.float32 and state.is_contiguous() and \
+            tuple(state.shape[1:]) == (taps - 1, Cc)
+    out = torch.empty(T, Cc, dtype=out_dtype or u.dtype, device=u.device)
+    p = _lib.CausalConvParams()
+    p.in_, p.ld_in, p.w, p.bias, p.state = _p(u), u.stride(0), _p(w), _p(bias), _p(state)
+    p.seqs, p.row_seq, p.out, p.ld_out = _i32(seqs, "seqs"), _i32(row_seq, "row_seq"), _p(out), out.stride(0)
+    p.in_dtype, p.w_dtype, p.out_dtype = _dt(u, "u"), _dt(w, "w"), _dt(out, "out")
+    p.rows, p.nseq, p.cols, p.taps, p.act = T, seqs.shape[0], Cc, taps, act
+    lib = _lib.load()
+    check(lib.vila_causal_conv_rows(C.byref(p), _stream()), "vila_causal_conv_rows")
+    if update_state and taps > 1:
+        check(lib.vila_causal_conv_state(C.byref(p), _stream()), "vila_causal_conv_state")
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, z: Optional[torch.Tensor], state: torch.Tensor, seqs: torch.Tensor,
+             *, heads: int, vdim: int, nstate: int, groups: int, dt_bias: torch.Tensor, A_log: torch.Tensor,
+             D: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    """Scalar-decay recurrence per head: S_t = exp(-exp(A_log) dt_t) S_{t-1} + dt_t B_t x_t^T, y_t = S_t^T C_t + D x_t,
+    dt_t = softplus(dt + dt_bias), out = y * silu(z).  xbc [T, heads*vdim + 2*groups*nstate] = x | B | C;
+    dt [T, heads]; z [T, heads*vdim] or None (views with a row stride are fine, one dtype for the three);
+    state fp32 [slots, heads, vdim, nstate], advanced in place; seqs int32 [n, 4] = (row0, rows, pos0, slot)."""
+    T = xbc.shape[0]
+    inner = heads * vdim
+    assert xbc.dim() == 2 and xbc.stride(1) == 1 and xbc.shape[1] == inner + 2 * groups * nstate
+    assert dt.shape == (T, heads) and dt.stride(1) == 1 and dt.dtype == xbc.dtype
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, nstate)
+    out = torch.empty(T, inner, dtype=out_dtype, device=xbc.device)
+    p = _lib.SsdScanParams()
+    p.xbc, p.ld_xbc, p.dt, p.ld_dt = _p(xbc), xbc.stride(0), _p(dt), dt.stride(0)
+    if z is not None:
+        assert z.shape == (T, inner) and z.stride(1) == 1 and z.dtype == xbc.dtype
+        p.z, p.ld_z = _p(z), z.stride(0)
+    p.dt_bias, p.A_log, p.D = _f32(dt_bias, "dt_bias"), _f32(A_log, "A_log"), _f32(D, "D")
+    assert dt_bias.numel() == heads and A_log.numel() == heads and D.numel() == heads
+    p.state, p.seqs, p.out, p.ld_out = _p(state), _i32(seqs, "seqs"), _p(out), out.stride(0)
+    p.in_dtype, p.out_dtype = _dt(xbc, "xbc"), _dt(out, "out")
+    p.nseq, p.H, p.P, p.N, p.G = seqs.shape[0], heads, vdim, nstate, groups
+    check(_lib.load().vila_ssd_scan(C.byref(p), _stream()), "vila_ssd_scan")
+    return out
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, z: Optional[torch.Tensor], state: torch.Tensor,
+                   seqs: torch.Tensor, *, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
+                   out_dtype=torch.float32) -> torch.Tensor:
+    """Per-channel selective recurrence: S_t[c, n] = exp(-exp(A_log[c, n]) dt_t,c) S_{t-1}[c, n] + dt_t,c x_t,c B_t,n,
+    y_t,c = sum_n S_t[c, n] C_t,n + D_c x_t,c, dt = softplus(dt + dt_bias), out = y * silu(z).  x, dt, z [T, C];
+    bc [T, 2 * N] = B | C (views with a row stride are fine, one dtype for all); state fp32 [slots, C, N]."""
+    T, Cc = x.shape
+    N = A_log.shape[1]
+    assert x.stride(1) == 1 and dt.shape == (T, Cc) and dt.stride(1) == 1 and dt.dtype == x.dtype
+    assert bc.shape == (T, 2 * N) and bc.stride(1) == 1 and bc.dtype == x.dtype
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (Cc, N)
+    assert A_log.shape == (Cc, N) and dt_bias.numel() == Cc and D.numel() == Cc
+    out = torch.empty(T, Cc, dtype=out_dtype, device=x.device)
+    p = _lib.SelectiveScanParams()
+    p.x, p.ld_x, p.dt, p.ld_dt, p.bc, p.ld_bc = _p(x), x.stride(0), _p(dt), dt.stride(0), _p(bc), bc.stride(0)
+    if z is not None:
+        assert z.shape == (T, Cc) and z.stride(1) == 1 and z.dtype == x.dtype
+        p.z, p.ld_z = _p(z), z.stride(0)
+    p.dt_bias, p.A_log, p.D = _f32(dt_bias, "dt_bias"), _f32(A_log, "A_log"), _f32(D, "D")
+    p.state, p.seqs, p.out, p.ld_out = _p(state), _i32(seqs, "seqs"), _p(out), out.stride(0)
+    p.in_dtype, p.out_dtype = _dt(x, "x"), _dt(out, "out")
+    p.nseq, p.C, p.N = seqs.shape[0], Cc, N
+    check(_lib.load().vila_selective_scan(C.byref(p), _stream()), "vila_selective_scan")
     return out
