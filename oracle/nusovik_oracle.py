@@ -169,10 +169,14 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, layer_output
     return h @ W["head"].T * config["logit_scale"]
 
 
-def greedy(config, weights, prompt, n_new: int) -> List[int]:
-    ids, out = list(prompt), []
+def greedy(config, weights, prompt, n_new: int):
+    """-> (new ids, top-2 logit margin of every choice)"""
+    ids, out, margins = list(prompt), [], []
     for _ in range(n_new):
-        tok = int(forward(config, weights, ids)[-1].argmax())
+        last = forward(config, weights, ids)[-1]
+        top = torch.topk(last, 2).values
+        tok = int(last.argmax())
         out.append(tok)
+        margins.append(float(top[0] - top[1]))
         ids.append(tok)
-    return out
+    return out, margins

@@ -280,8 +280,8 @@ class NusovikForCausalLM:
                 v = torch.randn(shape, generator=g, device=dev)
             elif last == "D":
                 v = 1.0 + torch.randn(shape, generator=g, device=dev) * 0.2
-            elif name.endswith("mix.dt"):
-                v = torch.randn(shape, generator=g, device=dev) * (scale / shape[1] ** 0.5)
+            elif name.endswith("mix.dt"):   # small step-size pre-activations: a decay exp(-a dt) multiplies their error by a
+                v = torch.randn(shape, generator=g, device=dev) * (0.2 / shape[1] ** 0.5)
             elif len(shape) == 2:
                 v = torch.randn(shape, generator=g, device=dev) * (scale / shape[1] ** 0.5)
             elif "norm" in name:
