@@ -1369,6 +1369,260 @@ def run_parallel_lm(args):
     res["gpu_launches"] = _lib.LAUNCHES
     print(json.dumps(res))
 
+# ------------------------------------------------------------------------------------------------
+# --workload ssm_lm: the Nusovik state-space / chunked-attention language model next to Moronex (the
+# closest model of the package: same engine, recurrent layers with an fp32 state per sequence beside
+# attention with sink and output gate, dense feed-forward) at equal width / depth / vocabulary,
+# random weights, bf16
+# ------------------------------------------------------------------------------------------------
+SSM_SIZES = {
+    "w1024": dict(width=1024, vocab=32768, heads=8, kv_heads=2, chunk=512, ff=4096, kv_rank=512, q_rank=384),
+    "w2048": dict(width=2048, vocab=32768, heads=16, kv_heads=4, chunk=512, ff=8192, kv_rank=512, q_rank=768),
+    "w4096": dict(width=4096, vocab=32768, heads=32, kv_heads=8, chunk=512, ff=16384, kv_rank=512, q_rank=1536),
+}
+
+
+def ssm_lm_config(z):
+    W = z["width"]
+    sel = {"conv": 4, "dt_rank": W // 16, "inner": 2 * W, "state": 16}
+    par = {"left": {"bias_max": 512, "dim": 128, "heads": z["heads"], "kv_heads": z["kv_heads"],
+                    "mask": {"size": z["chunk"]}, "scale": 128 ** -0.5, "vdim": 128},
+           "left_scale": 1.0,
+           "right": {"conv": 4, "groups": 8, "heads": 2 * W // 64, "norm_groups": 8, "state": 128, "vdim": 64},
+           "right_scale": 1.0}
+    ff = {"ff": z["ff"], "kind": "dense"}
+    layers = [{"type": "mamba1", "mixer": dict(sel), "mlp": None}, {"type": "parallel", "mixer": dict(par), "mlp": dict(ff)},
+              {"type": "mamba1", "mixer": dict(sel), "mlp": None}, {"type": "parallel", "mixer": dict(par), "mlp": dict(ff)}]
+    return {"architecture": "Nusovik", "embedding": {"scale": 1.0}, "layers": layers, "logit_scale": 1.0,
+            "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": W}
+
+
+def ssm_lm_twin(z):
+    """Moronex with the same width / heads / vocabulary: recurrent (HGRN2) and latent-attention layers in the same order"""
+    lat = dict(heads=z["heads"], dim=128, vdim=128, kv_rank=z["kv_rank"], q_rank=z["q_rank"], scale=128 ** -0.5)
+    rec = dict(heads=z["heads"], dim=128, vdim=128)
+    ff = {"kind": "dense", "ff": z["ff"] * 2 // 3 // 64 * 64}      # gated: three matrices of 2/3 the width
+    layers = [{"type": "hgrn2", "mixer": dict(rec), "mlp": None}, {"type": "latent_attention", "mixer": dict(lat), "mlp": dict(ff)},
+              {"type": "hgrn2", "mixer": dict(rec), "mlp": None}, {"type": "latent_attention", "mixer": dict(lat), "mlp": dict(ff)}]
+    return {"architecture": "Moronex", "layers": layers, "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
+
+
+def ssm_lm_block(args, peaks):
+    import torch
+
+    from vila_b200 import ops
+    from vila_b200.model import MoronexConfig, MoronexForCausalLM, NusovikConfig, NusovikForCausalLM
+    from vila_b200.serving import TokenEngine
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=args.steps, warm=max(3, args.warmup), setup=None):
+        ts = []
+        for i in range(warm + reps):
+            if setup is not None:
+                setup()
+            flush.fill_(i & 255)     # evict L2 (126 MB) between iterations
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def timed_op(fn):
+        """a single op of the kernel ledger: captured once, timed as a graph replay, so that the number is
+        the device time of its launches and not the host time of the Python call around them"""
+        fn()
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return timed(g.replay)
+
+    S, B, CTX, NEW = 2048, 8, 1024, 32
+    tf, gbs = peaks["bf16_tflops"], peaks["hbm_gbs"]
+    bf, f32 = torch.bfloat16, torch.float32
+    out = {}
+    t00 = time.time()
+
+    def log(msg):
+        print("[ssm_lm %6.1fs] %s" % (time.time() - t00, msg), file=sys.stderr, flush=True)
+
+    def engine_numbers(lm, prompt):
+        eng = TokenEngine(lm, max_tokens=B * (CTX + 4 * NEW + 64), slots=B)
+        t_pre = timed(lambda: eng.step([("p", prompt, [S - 1])]), setup=lambda: eng.release("p"))
+        eng.release("p")
+        for b in range(B):
+            eng.step([(b, prompt[:CTX], [])])
+        step_in = [[(b, [int(prompt[(k * 7 + b) % S])], [0]) for b in range(B)] for k in range(NEW)]
+
+        def decode_run():
+            for k in range(NEW):
+                eng.step(step_in[k])
+        t_dec = timed(decode_run, reps=3, warm=1)     # contexts grow CTX .. CTX + 4 * NEW: fits the reserve
+        for b in range(B):
+            eng.release(b)
+        n = sum(v.numel() for v in lm.weights.values())
+        return eng, {"params_m": n / 1e6, "prefill_tok_s": S / t_pre * 1e3, "prefill_ms": t_pre,
+                     "decode_tok_s": B * NEW / t_dec * 1e3, "decode_ms_per_step": t_dec / NEW}
+
+    def rate(t, flop=None, byts=None):
+        r = {"ms": t}
+        if flop is not None:
+            r["tflops_fp32"] = flop / t / 1e9
+        if byts is not None:
+            r["gbs"], r["of_hbm"] = byts / t / 1e6, byts / t / 1e6 / gbs
+        return r
+
+    for name, z in SSM_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        W, H, G = z["width"], z["heads"], z["kv_heads"]
+        g = torch.Generator().manual_seed(0)
+        prompt = torch.randint(0, z["vocab"], (S,), generator=g).tolist()
+        log("size %s: nusovik" % name)
+        cfgd = ssm_lm_config(z)
+        lm = NusovikForCausalLM(NusovikConfig.from_dict(cfgd), dev, bf).init_random(0, on_device=True)
+        eng, res_new = engine_numbers(lm, prompt)
+        log("size %s: moronex" % name)
+        tw = MoronexForCausalLM(MoronexConfig.from_dict(ssm_lm_twin(z)), dev, bf).init_random(0, on_device=True)
+        eng2, res_old = engine_numbers(tw, prompt)
+        # ---- kernel beside the like kernel ---------------------------------------------------------------
+        log("kernel ledger")
+        led = {}
+        Ls, Lp, Mr, Ma = lm.layers[0], lm.layers[1], tw.layers[0], tw.layers[1]
+        sq1 = torch.tensor([[0, S, 0, 0]], dtype=torch.int32, device=dev)
+        sqB = torch.tensor([(b, 1, CTX, b) for b in range(B)], dtype=torch.int32, device=dev)
+        rs1 = torch.zeros(S, dtype=torch.int32, device=dev)
+        # recurrences: one 2048-row prompt, and 8 decoded rows
+        r = cfgd["layers"][1]["mixer"]["right"]
+        Hs, P, N, Gs = r["heads"], r["vdim"], r["state"], r["groups"]
+        inner, chans = Hs * P, Hs * P + 2 * Gs * N
+        wide = (torch.randn(S, 2 * inner + 2 * Gs * N + Hs, device=dev) * 0.5).to(bf)
+        st = eng.cache.state[(1, "ssm")]
+        skw = dict(heads=Hs, vdim=P, nstate=N, groups=Gs, dt_bias=Lp.dt_bias, A_log=Lp.A_log, D=Lp.D)
+        for rows, sq, tag in ((S, sq1, "prefill, one %d-row prompt" % S), (B, sqB, "decode, %d rows" % B)):
+            t = timed_op(lambda: ops.ssd_scan(wide[:rows, inner:inner + chans], wide[:rows, inner + chans:inner + chans + Hs],
+                                              wide[:rows, :inner], st, sq, **skw))
+            nseq = sq.shape[0]
+            led["ssd_scan " + tag] = rate(t, flop=6.0 * rows * Hs * P * N,
+                                          byts=rows * (2 * inner + chans + Hs) * 2 + rows * inner * 4 + 2 * nseq * Hs * P * N * 4)
+        m1 = cfgd["layers"][0]["mixer"]
+        C1, N1 = m1["inner"], m1["state"]
+        xs, dts, zs = [(torch.randn(S, C1, device=dev) * 0.5).to(bf) for _ in range(3)]
+        bc = (torch.randn(S, 2 * N1, device=dev) * 0.5).to(bf)
+        st1 = eng.cache.state[(0, "ssm")]
+        for rows, sq, tag in ((S, sq1, "prefill, one %d-row prompt" % S), (B, sqB, "decode, %d rows" % B)):
+            t = timed_op(lambda: ops.selective_scan(xs[:rows], dts[:rows], bc[:rows], zs[:rows], st1, sq, dt_bias=Ls.dt_bias,
+                                                    A_log=Ls.A_log, D=Ls.D, out_dtype=bf))
+            nseq = sq.shape[0]
+            led["selective_scan " + tag] = rate(t, flop=6.0 * rows * C1 * N1,
+                                                byts=rows * (4 * C1 + 2 * N1) * 2 + 2 * nseq * C1 * N1 * 4)
+        proj = (torch.randn(S, 3 * H * 128 + W, device=dev) * 0.5).to(bf)
+        st2 = eng2.cache.state[0]
+        for rows, sq, tag in ((S, sq1, "prefill, one %d-row prompt" % S), (B, sqB, "decode, %d rows" % B)):
+            t = timed_op(lambda: ops.hgrn2_scan(proj[:rows], st2, sq, heads=H, dim=128, vdim=128, q_off=0, f_off=H * 128,
+                                                v_off=2 * H * 128, f_bias=Mr.f_bias, lower=Mr.lower))
+            nseq = sq.shape[0]
+            led["moronex hgrn2_scan " + tag] = rate(t, flop=6.0 * rows * H * 128 * 128,
+                                                    byts=rows * 3 * H * 128 * 2 + rows * H * 128 * 4 + 2 * nseq * H * 128 * 128 * 4)
+        # attention: the same paged kernel with and without this model's options, and Moronex's un-folded kernel
+        page, npg = eng.cache.page, eng.cache.n_pages
+        pool = eng.cache.latent[1]
+        pt = torch.arange(npg, dtype=torch.int32, device=dev).view(1, -1).repeat(B, 1).contiguous()
+        tiles = torch.tensor([(o, 16, o, 0) for o in range(0, S, 16)], dtype=torch.int32, device=dev)
+        q = torch.randn(S, H * 128, device=dev)
+        gate = torch.randn(S, H, device=dev).to(bf)
+        akw = dict(heads=H, kv_heads=G, dim=128, vdim=128, page=page, scale=0.088, sink=Lp.sink)
+        okw = dict(dist_bias=Lp.dist_bias, chunk=z["chunk"], gate=gate)
+        ck = z["chunk"]
+        pairs_chunk = sum((p % ck) + 1 for p in range(S))
+        t = timed_op(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, **akw, **okw))
+        led["paged_attention prefill, chunk %d + distance bias + gate" % ck] = rate(t, flop=H * pairs_chunk * 4.0 * 128)
+        t = timed_op(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, **akw))
+        led["paged_attention prefill, plain causal (the kernel as the rotary GQA model uses it)"] = rate(
+            t, flop=H * (S * (S + 1) / 2) * 4.0 * 128)
+        kvb = torch.randn(S, H * 256, device=dev).to(bf)
+        qb = torch.randn(S, H * 128, device=dev).to(bf)
+        t = timed_op(lambda: ops.sink_attention(qb, kvb[:, :H * 128], kvb[:, H * 128:], tiles, heads=H, scale=0.088,
+                                                sink=Ma.sink, gate=gate))
+        led["moronex sink_attention prefill (un-folded, plain causal)"] = rate(t, flop=H * (S * (S + 1) / 2) * 4.0 * 128)
+        dt_ = torch.tensor([(b, 1, CTX - 1, b) for b in range(B)], dtype=torch.int32, device=dev)
+        pt2 = ((torch.arange(B, device=dev, dtype=torch.int32)[:, None] * (CTX // page) +
+                torch.arange(npg, device=dev, dtype=torch.int32)[None]) % npg).contiguous()
+        okd = dict(okw, gate=gate[:B])
+        t = timed_op(lambda: ops.paged_attention(q[:B], pool, pt2, dt_, max_rows=1, nsplit=eng.cache.decode_splits, **akw, **okd))
+        led["paged_attention decode, chunk %d (8 rows at position %d: %d keys each)" % (ck, CTX - 1, (CTX - 1) % ck + 1)] = rate(
+            t, byts=B * ((CTX - 1) % ck + 1) * G * 256 * 2)
+        t = timed_op(lambda: ops.paged_attention(q[:B], pool, pt2, dt_, max_rows=1, nsplit=eng.cache.decode_splits, **akw))
+        led["paged_attention decode, plain causal (8 x 1024 keys)"] = rate(t, byts=B * CTX * G * 256 * 2)
+        # row kernels
+        x = torch.randn(S, W, device=dev)
+        y1, y2 = torch.randn(S, W, device=dev).to(bf), torch.randn(S, W, device=dev).to(bf)
+        t = timed_op(lambda: ops.branch_norm_residual(x, y1, Lp.norm1, 1e-5, a_scale=1.0, b=y2, b_scale=1.0, copy_dtype=bf))
+        led["branch_norm_residual, two branches + bf16 copy (2048 rows)"] = rate(t, byts=S * W * (8 + 2 + 2 + 2))
+        gt = torch.randn(S, W, device=dev).to(bf)
+        t = timed_op(lambda: ops.gated_norm_residual(x, y1, gate=gt, gate_bias=Ma.rg1_b, w=Ma.norm1b, w_offset=1.0, eps=1e-5))
+        led["moronex gated_norm_residual (2048 rows)"] = rate(t, byts=S * W * (8 + 2 + 2))
+        cst = eng.cache.state[(1, "conv")]
+        t = timed_op(lambda: ops.causal_conv_rows(wide[:, inner:inner + chans], Lp.ssd_conv, Lp.ssd_conv_b, cst, sq1, rs1,
+                                                  act=ops.CONV_SILU, out_dtype=bf))
+        led["causal_conv_rows + tail update, %d channels, 4 taps, SiLU (2048 rows)" % chans] = rate(t, byts=S * chans * 4)
+        h32 = torch.randn(S, W, device=dev)
+        cw = torch.randn(W, 4, device=dev)
+        cst2 = torch.zeros(B, 3, W, device=dev)
+        t = timed_op(lambda: ops.short_conv_rows(h32, cw, cst2, sq1, rs1, out_dtype=bf))
+        led["short_conv_rows + state, %d channels, 4 taps (the parallel-sublayer model's, fp32 in, 2048 rows)" % W] = rate(
+            t, byts=S * W * 6)
+        ar = torch.arange(S, dtype=torch.int32, device=dev)
+        t = timed_op(lambda: ops.embed_sincos_rows(lm.embed, ar, ar, lm.inv_freq, 1.0, copy_dtype=bf))
+        led["embed_sincos_rows (2048 rows)"] = rate(t, byts=S * W * (2 + 4 + 2))
+        t = timed_op(lambda: ops.embed_rows(tw.embed, ar))
+        led["moronex embed_rows (2048 rows)"] = rate(t, byts=S * W * (2 + 4))
+        qk = (torch.randn(S, (H + G) * 128 + 8, device=dev)).to(bf)
+        t = timed_op(lambda: ops.rope_append(qk, ar, ar, pool, heads=H, kv_heads=G, dim=128, vdim=128, inv_freq=None,
+                                             unit_norm=True, eps=1e-5, q_norm_w=Lp.q_norm, k_norm_w=Lp.k_norm, v_from_k=True))
+        led["head norm + k | v append (2048 rows)"] = rate(t, byts=S * ((H + G) * 128 * 2 + H * 128 * 4 + 2 * G * 128 * 2))
+        # feed-forward: the tensor-core GEMM with the squared-ReLU epilogue beside the gated one
+        hb = torch.randn(S, W, device=dev).to(bf)
+        t = timed_op(lambda: ops.linear_any(hb, Lp.up, act=ops.ACT_RELU2))
+        fl = 2.0 * S * W * z["ff"]
+        led["feed-forward up-projection, squared-ReLU epilogue (tcgen05)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        t = timed_op(lambda: ops.linear_any(hb, Ma.gu, swiglu=True))
+        fl = 2.0 * S * W * Ma.gu.shape[0]
+        led["moronex feed-forward gate|up projection, SwiGLU epilogue (tcgen05)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        out[name] = {"nusovik": res_new, "moronex": res_old, "kernels": led}
+        del lm, tw, eng, eng2
+        torch.cuda.empty_cache()
+    return {"workload": "ssm_lm: 4 Nusovik layers (selective scan; chunked sink attention + scalar-decay scan in parallel + "
+                        "squared-ReLU feed-forward; twice) vs 4 Moronex layers (HGRN2; latent attention + gated feed-forward; "
+                        "twice) of equal width / heads / vocabulary; prefill: one %d-token prompt; decode: %d sequences x "
+                        "%d-token context, %d steps" % (S, B, CTX, NEW),
+            "dtype": "bf16", "data": "synthetic (random weights, random ids)",
+            "l2_policy": "256 MB buffer written between timed iterations",
+            "kernel_ledger_timing": "each op captured in a CUDA graph, one replay per timed iteration", "peaks": peaks, "sizes": out}
+
+
+def run_ssm_lm(args):
+    import torch
+    assert torch.cuda.is_available(), "bench.py --workload ssm_lm needs a GPU"
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("VILA_BENCH_WATCHDOG_S", "480")), exit=True)
+    peaks = read_peaks()
+    with ClockSampler(0) as cs:
+        res = ssm_lm_block(args, peaks)
+    res["clocks"] = cs.summary()
+    from vila_b200 import _lib
+    res["gpu_launches"] = _lib.LAUNCHES
+    print(json.dumps(res))
+
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -1384,16 +1638,18 @@ def main():
     ap.add_argument("--sp-steps", type=int, default=10)
     ap.add_argument("--profile", action="store_true",
                     help="profiling aid (ncu): 1 warm-up, 8 new tokens, no extra blocks; NOT a valid bench number")
-    ap.add_argument("--sizes", default="", help="hybrid_lm / parallel_lm: comma-separated subset of the workload's sizes ("
+    ap.add_argument("--sizes", default="", help="hybrid_lm / parallel_lm / ssm_lm: comma-separated subset of the workload's sizes ("
                     + ",".join(HYBRID_SIZES) + " / " + ",".join(PARALLEL_SIZES) + ")")
-    ap.add_argument("--workload", default="headline", choices=["headline", "hybrid_lm", "parallel_lm"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "hybrid_lm", "parallel_lm", "ssm_lm"],
                     help="headline (default): the NVILA-8B serving step; hybrid_lm: Moronex vs Qwen2 at equal size; "
-                         "parallel_lm: Lufatar vs Moronex at equal size")
+                         "parallel_lm: Lufatar vs Moronex at equal size; ssm_lm: Nusovik vs Moronex at equal size")
     args = ap.parse_args()
     if args.workload == "hybrid_lm":
         return run_hybrid_lm(args)
     if args.workload == "parallel_lm":
         return run_parallel_lm(args)
+    if args.workload == "ssm_lm":
+        return run_ssm_lm(args)
     if args.profile:
         global NEW_TOKENS
         NEW_TOKENS = 8

@@ -13,7 +13,8 @@
 //                       thread (column c = tid / 8, r = tid % 8) keeps the state entries n = r * KPT .. of
 //                       its column in registers (state layout [.., P, N]: a thread's entries are
 //                       contiguous, 8 lanes cover a column's N), the sum over n ends with three shuffles.
-//                       16 tokens at a time are staged in shared memory with softplus / exp evaluated once
+//                       16 tokens at a time are staged in shared memory with softplus / exp evaluated once,
+//                       the next 16 are fetched into registers meanwhile, outputs leave through shared memory
 //   selective_scan      S_t[c, n] = exp(dt_t,c A[c, n]) S_{t-1}[c, n] + dt_t,c x_t,c B_t,n,  y = S C + D x; grid
 //                       (sequence, 32 channels); thread (channel, r) as above, A[c, n] in registers
 // softplus, exponentials, decays, step sizes, states and sums are fp32 whatever the tensors' dtype; time
@@ -104,26 +105,30 @@ __global__ void __launch_bounds__(kThreads) causal_conv_state_kernel(const vila_
   }
 }
 
-// Shared-memory position of state index n when a thread owns KPT consecutive entries: 4 floats of padding
-// per owner, so that the 8 owners' float4 reads fall into different banks.
-template <int KPT>
-__device__ __forceinline__ int pad_idx(int n) { return n + (n / KPT) * 4; }
-
 // ---- scalar-decay recurrence (state-space duality form) ----------------------------------------------
+// Both scans keep global memory out of the time loop: the inputs of 16 tokens are fetched into registers
+// while the previous 16 are being processed, go to shared memory with softplus / exp / silu evaluated once,
+// and the outputs of the 16 tokens leave through shared memory after the loop.
 template <int KPT>   // state entries per thread: N <= 8 * KPT, KPT a multiple of 4
 __global__ void __launch_bounds__(kThreads) ssd_scan_kernel(const vila_ssd_scan_params p) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int NS = kLanes * (KPT + 4);         // padded floats per token for B or C
+  constexpr int NP = kLanes * KPT;               // state entries the 8 owners cover
+  constexpr int NS = kLanes * (KPT + 4);         // padded floats per token for B or C: 4 per owner, so that the
+                                                 // owners' float4 reads fall into different banks
+  constexpr int BCN = kChunk * NP / kThreads;    // B (or C) entries a thread stages per round
+  constexpr int XN = kChunk * kCols / kThreads;  // x (or z) entries a thread stages per round
   float* B_s = sm;                               // [kChunk][NS]
   float* C_s = B_s + kChunk * NS;                // [kChunk][NS]
   float* x_s = C_s + kChunk * NS;                // [kChunk][kCols]
-  float* dt_s = x_s + kChunk * kCols;            // [kChunk]
+  float* z_s = x_s + kChunk * kCols;             // [kChunk][kCols] silu(z), or 1
+  float* y_s = z_s + kChunk * kCols;             // [kChunk][kCols]
+  float* dt_s = y_s + kChunk * kCols;            // [kChunk]
   float* a_s = dt_s + kChunk;                    // [kChunk]
   const int tid = threadIdx.x, r = tid & (kLanes - 1), c = tid >> 3;
   const int* sq = p.seqs + 4 * blockIdx.x;
   const int row0 = sq[0], n = sq[1], pos0 = sq[2], slot = sq[3];
   const int h = blockIdx.y, P = p.P, N = p.N, g = h / (p.H / p.G);
-  const int col = blockIdx.z * kCols + c;
+  const int col0 = blockIdx.z * kCols, col = col0 + c;
   const bool col_ok = col < P;
   const int n0 = r * KPT;                        // first state index of this thread
   float* st = p.state + ((static_cast<size_t>(slot) * p.H + h) * P + (col_ok ? col : 0)) * N;
@@ -133,25 +138,52 @@ __global__ void __launch_bounds__(kThreads) ssd_scan_kernel(const vila_ssd_scan_
   const float neg_a = -expf(p.A_log[h]), bias = p.dt_bias[h], Dh = p.D[h];
   const size_t xoff = static_cast<size_t>(h) * P, boff = static_cast<size_t>(p.H) * P + static_cast<size_t>(g) * N;
   const size_t coff = boff + static_cast<size_t>(p.G) * N;
+  uint32_t rb[BCN], rc[BCN], rx[XN], rz[XN], rdt = 0u;   // raw bits: converted when they go to shared memory
+  const int dt_in = p.in_dtype;
+  auto fetch = [&](int t0) {
+    const int nt = min(kChunk, n - t0);
+#pragma unroll
+    for (int k = 0; k < BCN; ++k) {
+      const int idx = tid + k * kThreads, t = idx / NP, i = idx - t * NP;
+      const bool ok = t < nt && i < N;
+      const size_t base = static_cast<size_t>(row0 + t0 + t) * p.ld_xbc;
+      rb[k] = ok ? ld_raw(p.xbc, dt_in, base + boff + i) : 0u;
+      rc[k] = ok ? ld_raw(p.xbc, dt_in, base + coff + i) : 0u;
+    }
+#pragma unroll
+    for (int k = 0; k < XN; ++k) {
+      const int idx = tid + k * kThreads, t = idx / kCols, gc = col0 + (idx - t * kCols);
+      const bool ok = t < nt && gc < P;
+      const size_t row = static_cast<size_t>(row0 + t0 + t);
+      rx[k] = ok ? ld_raw(p.xbc, dt_in, row * p.ld_xbc + xoff + gc) : 0u;
+      rz[k] = (ok && p.z) ? ld_raw(p.z, dt_in, row * p.ld_z + xoff + gc) : 0u;
+    }
+    if (tid < kChunk) rdt = tid < nt ? ld_raw(p.dt, dt_in, static_cast<size_t>(row0 + t0 + tid) * p.ld_dt + h) : 0u;
+  };
+  fetch(0);
   for (int t0 = 0; t0 < n; t0 += kChunk) {
     const int nt = min(kChunk, n - t0);
     __syncthreads();
-    for (int idx = tid; idx < nt * kLanes * KPT; idx += kThreads) {
-      const int t = idx / (kLanes * KPT), i = idx - t * (kLanes * KPT);
-      const size_t base = static_cast<size_t>(row0 + t0 + t) * p.ld_xbc;
-      B_s[t * NS + pad_idx<KPT>(i)] = i < N ? ld_any(p.xbc, p.in_dtype, base + boff + i) : 0.f;
-      C_s[t * NS + pad_idx<KPT>(i)] = i < N ? ld_any(p.xbc, p.in_dtype, base + coff + i) : 0.f;
+#pragma unroll
+    for (int k = 0; k < BCN; ++k) {
+      const int idx = tid + k * kThreads, t = idx / NP, i = idx - t * NP;
+      const int at = t * NS + i + (i / KPT) * 4;
+      B_s[at] = raw_to_float(rb[k], dt_in);
+      C_s[at] = raw_to_float(rc[k], dt_in);
     }
-    for (int idx = tid; idx < nt * kCols; idx += kThreads) {
-      const int t = idx / kCols, cc = idx - t * kCols, gc = blockIdx.z * kCols + cc;
-      x_s[idx] = gc < P ? ld_any(p.xbc, p.in_dtype, static_cast<size_t>(row0 + t0 + t) * p.ld_xbc + xoff + gc) : 0.f;
+#pragma unroll
+    for (int k = 0; k < XN; ++k) {
+      const int idx = tid + k * kThreads;
+      x_s[idx] = raw_to_float(rx[k], dt_in);
+      z_s[idx] = p.z ? silu_exact_f(raw_to_float(rz[k], dt_in)) : 1.0f;
     }
-    if (tid < nt) {
-      const float dt = softplus_f(ld_any(p.dt, p.in_dtype, static_cast<size_t>(row0 + t0 + tid) * p.ld_dt + h) + bias);
+    if (tid < kChunk) {
+      const float dt = softplus_f(raw_to_float(rdt, dt_in) + bias);
       dt_s[tid] = dt;
       a_s[tid] = expf(neg_a * dt);
     }
     __syncthreads();
+    if (t0 + kChunk < n) fetch(t0 + kChunk);     // in flight while this round is processed
     for (int t = 0; t < nt; ++t) {
       const float x = x_s[t * kCols + c], dt = dt_s[t], a = a_s[t];
       const float xdt = dt * x;
@@ -174,12 +206,12 @@ __global__ void __launch_bounds__(kThreads) ssd_scan_kernel(const vila_ssd_scan_
       y += __shfl_xor_sync(0xffffffffu, y, 1);
       y += __shfl_xor_sync(0xffffffffu, y, 2);
       y += __shfl_xor_sync(0xffffffffu, y, 4);
-      if (r == 0 && col_ok) {
-        const size_t row = static_cast<size_t>(row0 + t0 + t);
-        float o = fmaf(Dh, x, y);
-        if (p.z) o *= silu_exact_f(ld_any(p.z, p.in_dtype, row * p.ld_z + xoff + col));
-        st_any(p.out, p.out_dtype, row * p.ld_out + xoff + col, o);
-      }
+      if (r == 0) y_s[t * kCols + c] = fmaf(Dh, x, y) * z_s[t * kCols + c];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nt * kCols; idx += kThreads) {
+      const int t = idx / kCols, gc = col0 + (idx - t * kCols);
+      if (gc < P) st_any(p.out, p.out_dtype, static_cast<size_t>(row0 + t0 + t) * p.ld_out + xoff + gc, y_s[idx]);
     }
   }
   if (col_ok) {
@@ -193,16 +225,21 @@ __global__ void __launch_bounds__(kThreads) ssd_scan_kernel(const vila_ssd_scan_
 template <int KPT>   // state entries per thread: N <= 8 * KPT
 __global__ void __launch_bounds__(kThreads) selective_scan_kernel(const vila_selective_scan_params p) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int KP = KPT >= 4 ? KPT + 4 : KPT;   // padded entries per owner (float4 reads need KPT >= 4)
+  constexpr int NP = kLanes * KPT;
+  constexpr int KP = KPT >= 4 ? KPT + 4 : KPT;   // padded entries per owner
   constexpr int NS = kLanes * KP;
+  constexpr int BCN = (kChunk * NP + kThreads - 1) / kThreads;
+  constexpr int XN = kChunk * kCols / kThreads;
   float* B_s = sm;                               // [kChunk][NS]
   float* C_s = B_s + kChunk * NS;                // [kChunk][NS]
   float* x_s = C_s + kChunk * NS;                // [kChunk][kCols]
   float* dt_s = x_s + kChunk * kCols;            // [kChunk][kCols]
+  float* z_s = dt_s + kChunk * kCols;            // [kChunk][kCols] silu(z), or 1
+  float* y_s = z_s + kChunk * kCols;             // [kChunk][kCols]
   const int tid = threadIdx.x, r = tid & (kLanes - 1), c = tid >> 3;
   const int* sq = p.seqs + 4 * blockIdx.x;
   const int row0 = sq[0], n = sq[1], pos0 = sq[2], slot = sq[3];
-  const int N = p.N, ch = blockIdx.y * kCols + c;
+  const int N = p.N, ch0 = blockIdx.y * kCols, ch = ch0 + c;
   const bool ch_ok = ch < p.C;
   const int n0 = r * KPT;
   float* st = p.state + (static_cast<size_t>(slot) * p.C + (ch_ok ? ch : 0)) * N;
@@ -214,24 +251,56 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(const vila_sel
     A[k] = ok ? -expf(p.A_log[static_cast<size_t>(ch) * N + n0 + k]) : 0.f;
   }
   const float Dc = ch_ok ? p.D[ch] : 0.f;
+  uint32_t rb[BCN], rc[BCN], rx[XN], rd[XN], rz[XN];     // raw bits: converted when they go to shared memory
+  const int dt_in = p.in_dtype;
+  float dbias[XN];                                       // a thread stages the same channels in every round
+#pragma unroll
+  for (int k = 0; k < XN; ++k) {
+    const int gc = ch0 + (tid + k * kThreads) % kCols;
+    dbias[k] = gc < p.C ? p.dt_bias[gc] : 0.f;
+  }
+  auto fetch = [&](int t0) {
+    const int nt = min(kChunk, n - t0);
+#pragma unroll
+    for (int k = 0; k < BCN; ++k) {
+      const int idx = tid + k * kThreads, t = idx / NP, i = idx - t * NP;
+      const bool ok = t < nt && i < N;              // t < nt <= kChunk also bounds idx
+      const size_t base = static_cast<size_t>(row0 + t0 + t) * p.ld_bc;
+      rb[k] = ok ? ld_raw(p.bc, dt_in, base + i) : 0u;
+      rc[k] = ok ? ld_raw(p.bc, dt_in, base + N + i) : 0u;
+    }
+#pragma unroll
+    for (int k = 0; k < XN; ++k) {
+      const int idx = tid + k * kThreads, t = idx / kCols, gc = ch0 + (idx - t * kCols);
+      const bool ok = t < nt && gc < p.C;
+      const size_t row = static_cast<size_t>(row0 + t0 + t);
+      rx[k] = ok ? ld_raw(p.x, dt_in, row * p.ld_x + gc) : 0u;
+      rd[k] = ok ? ld_raw(p.dt, dt_in, row * p.ld_dt + gc) : 0u;
+      rz[k] = (ok && p.z) ? ld_raw(p.z, dt_in, row * p.ld_z + gc) : 0u;
+    }
+  };
+  fetch(0);
   for (int t0 = 0; t0 < n; t0 += kChunk) {
     const int nt = min(kChunk, n - t0);
     __syncthreads();
-    for (int idx = tid; idx < nt * kLanes * KPT; idx += kThreads) {
-      const int t = idx / (kLanes * KPT), i = idx - t * (kLanes * KPT);
-      const size_t base = static_cast<size_t>(row0 + t0 + t) * p.ld_bc;
-      const int at = t * NS + (i / KPT) * KP + (i % KPT);
-      B_s[at] = i < N ? ld_any(p.bc, p.in_dtype, base + i) : 0.f;
-      C_s[at] = i < N ? ld_any(p.bc, p.in_dtype, base + N + i) : 0.f;
+#pragma unroll
+    for (int k = 0; k < BCN; ++k) {
+      const int idx = tid + k * kThreads, t = idx / NP, i = idx - t * NP;
+      if (idx < kChunk * NP) {
+        const int at = t * NS + (i / KPT) * KP + (i % KPT);
+        B_s[at] = raw_to_float(rb[k], dt_in);
+        C_s[at] = raw_to_float(rc[k], dt_in);
+      }
     }
-    for (int idx = tid; idx < nt * kCols; idx += kThreads) {
-      const int t = idx / kCols, cc = idx - t * kCols, gc = blockIdx.y * kCols + cc;
-      const size_t row = static_cast<size_t>(row0 + t0 + t);
-      const bool ok = gc < p.C;
-      x_s[idx] = ok ? ld_any(p.x, p.in_dtype, row * p.ld_x + gc) : 0.f;
-      dt_s[idx] = ok ? softplus_f(ld_any(p.dt, p.in_dtype, row * p.ld_dt + gc) + p.dt_bias[gc]) : 0.f;
+#pragma unroll
+    for (int k = 0; k < XN; ++k) {
+      const int idx = tid + k * kThreads;
+      x_s[idx] = raw_to_float(rx[k], dt_in);
+      dt_s[idx] = softplus_f(raw_to_float(rd[k], dt_in) + dbias[k]);
+      z_s[idx] = p.z ? silu_exact_f(raw_to_float(rz[k], dt_in)) : 1.0f;
     }
     __syncthreads();
+    if (t0 + kChunk < n) fetch(t0 + kChunk);     // in flight while this round is processed
     for (int t = 0; t < nt; ++t) {
       const float x = x_s[t * kCols + c], dt = dt_s[t * kCols + c];
       const float xdt = dt * x;
@@ -248,12 +317,12 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(const vila_sel
       y += __shfl_xor_sync(0xffffffffu, y, 1);
       y += __shfl_xor_sync(0xffffffffu, y, 2);
       y += __shfl_xor_sync(0xffffffffu, y, 4);
-      if (r == 0 && ch_ok) {
-        const size_t row = static_cast<size_t>(row0 + t0 + t);
-        float o = fmaf(Dc, x, y);
-        if (p.z) o *= silu_exact_f(ld_any(p.z, p.in_dtype, row * p.ld_z + ch));
-        st_any(p.out, p.out_dtype, row * p.ld_out + ch, o);
-      }
+      if (r == 0) y_s[t * kCols + c] = fmaf(Dc, x, y) * z_s[t * kCols + c];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nt * kCols; idx += kThreads) {
+      const int t = idx / kCols, gc = ch0 + (idx - t * kCols);
+      if (gc < p.C) st_any(p.out, p.out_dtype, static_cast<size_t>(row0 + t0 + t) * p.ld_out + gc, y_s[idx]);
     }
   }
   if (ch_ok) {
@@ -298,7 +367,7 @@ int ssd_scan(const vila_ssd_scan_params& p, cudaStream_t stream) {
   VB_CHECK(grid.y <= 65535 && grid.z <= 65535, "ssd_scan: grid too large");
 #define VB_SSD(KPT)                                                                                         \
   VB_CUDA(launch_serial(ssd_scan_kernel<KPT>, grid, dim3(kThreads),                                         \
-                        sizeof(float) * (2 * kChunk * kLanes * (KPT + 4) + kChunk * kCols + 2 * kChunk), stream, p))
+                        sizeof(float) * (2 * kChunk * kLanes * (KPT + 4) + 3 * kChunk * kCols + 2 * kChunk), stream, p))
   if (p.N <= 32) VB_SSD(4);
   else if (p.N <= 64) VB_SSD(8);
   else if (p.N <= 128) VB_SSD(16);
@@ -314,7 +383,7 @@ int selective_scan(const vila_selective_scan_params& p, cudaStream_t stream) {
   VB_CHECK(grid.y <= 65535, "selective_scan: C=%d", p.C);
 #define VB_SEL(KPT)                                                                                          \
   VB_CUDA(launch_serial(selective_scan_kernel<KPT>, grid, dim3(kThreads),                                    \
-                        sizeof(float) * (2 * kChunk * kLanes * (KPT >= 4 ? KPT + 4 : KPT) + 2 * kChunk * kCols), \
+                        sizeof(float) * (2 * kChunk * kLanes * (KPT >= 4 ? KPT + 4 : KPT) + 4 * kChunk * kCols), \
                         stream, p))
   if (p.N <= 8) VB_SEL(1);
   else if (p.N <= 16) VB_SEL(2);
