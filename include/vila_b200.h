@@ -584,8 +584,8 @@ int vila_gelu_mul_gather(const void* z, int z_dtype, const void* table, int tabl
  * recurrences, and the post-normed residual update of two scaled branches. ------------------------- */
 
 /* out[t, c] = table[ids[t], c] * scale + (c odd ? cos : sin)(positions[t] * inv_freq[c / 2])
- * inv_freq fp64 [(cols + 1) / 2]; the angle is formed in double.  copy (may be NULL) also receives the
- * rows in copy_dtype. */
+ * inv_freq fp64 [(cols + 1) / 2]; the angle is formed and reduced to [-pi, pi] in double.  copy (may be NULL)
+ * also receives the rows in copy_dtype. */
 int vila_embed_sincos_rows(const void* table, int table_dtype, const int32_t* ids, const int32_t* positions,
                            const double* inv_freq, float scale, float* out, void* copy, int copy_dtype,
                            int rows, int cols, void* stream);

@@ -355,8 +355,9 @@ inline int flat_grid(size_t total) {
 }
 
 // ---- scaled embedding + sinusoidal positions ---------------------------------------------------------
-// A warp per row; a lane takes column pairs (2i, 2i + 1) = (sin, cos) of ONE angle position * inv_freq[i],
-// formed and evaluated in double so that far positions keep their phase.
+// A warp per row; a lane takes column pairs (2i, 2i + 1) = (sin, cos) of ONE angle position * inv_freq[i].
+// The angle is formed and brought into [-pi, pi] in double, so that far positions keep their phase (an fp32
+// product loses it); sine and cosine of the reduced angle are evaluated in fp32.
 __global__ void __launch_bounds__(kRowThreads)
 embed_sincos_rows_kernel(const void* __restrict__ table, int dt, const int32_t* __restrict__ ids,
                          const int32_t* __restrict__ positions, const double* __restrict__ inv_freq, float scale,
@@ -366,13 +367,15 @@ embed_sincos_rows_kernel(const void* __restrict__ table, int dt, const int32_t* 
   const size_t src = static_cast<size_t>(ids[row]) * cols, dst = static_cast<size_t>(row) * cols;
   const double pos = static_cast<double>(positions[row]);
   for (int i = lane_id(); 2 * i < cols; i += 32) {
-    double sn, cs;
-    sincos(pos * inv_freq[i], &sn, &cs);
-    const float v0 = fmaf(ld_any(table, dt, src + 2 * i), scale, static_cast<float>(sn));
+    const double ang = pos * inv_freq[i];
+    const float red = static_cast<float>(fma(-6.283185307179586476925, rint(ang * 0.15915494309189533577), ang));
+    float sn, cs;
+    sincosf(red, &sn, &cs);
+    const float v0 = fmaf(ld_any(table, dt, src + 2 * i), scale, sn);
     out[dst + 2 * i] = v0;
     if (copy) st_any(copy, c_dt, dst + 2 * i, v0);
     if (2 * i + 1 < cols) {
-      const float v1 = fmaf(ld_any(table, dt, src + 2 * i + 1), scale, static_cast<float>(cs));
+      const float v1 = fmaf(ld_any(table, dt, src + 2 * i + 1), scale, cs);
       out[dst + 2 * i + 1] = v1;
       if (copy) st_any(copy, c_dt, dst + 2 * i + 1, v1);
     }
