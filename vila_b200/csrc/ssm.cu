@@ -31,7 +31,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kMaxTaps = 16;
 constexpr int kConvRows = 8;
-constexpr int kChunk = 16;      // tokens staged per round of a scan
+constexpr int kChunk = 16;      // tokens staged per stage of a scan
 constexpr int kLanes = 8;       // threads that share a state column / channel
 constexpr int kCols = kThreads / kLanes;
 
@@ -115,8 +115,8 @@ __global__ void __launch_bounds__(kThreads) ssd_scan_kernel(const vila_ssd_scan_
   constexpr int NP = kLanes * KPT;               // state entries the 8 owners cover
   constexpr int NS = kLanes * (KPT + 4);         // padded floats per token for B or C: 4 per owner, so that the
                                                  // owners' float4 reads fall into different banks
-  constexpr int BCN = kChunk * NP / kThreads;    // B (or C) entries a thread stages per round
-  constexpr int XN = kChunk * kCols / kThreads;  // x (or z) entries a thread stages per round
+  constexpr int BCN = kChunk * NP / kThreads;    // B (or C) entries a thread brings in per stage
+  constexpr int XN = kChunk * kCols / kThreads;  // x (or z) entries a thread brings in per stage
   float* B_s = sm;                               // [kChunk][NS]
   float* C_s = B_s + kChunk * NS;                // [kChunk][NS]
   float* x_s = C_s + kChunk * NS;                // [kChunk][kCols]
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(kThreads) ssd_scan_kernel(const vila_ssd_scan_
       a_s[tid] = expf(neg_a * dt);
     }
     __syncthreads();
-    if (t0 + kChunk < n) fetch(t0 + kChunk);     // in flight while this round is processed
+    if (t0 + kChunk < n) fetch(t0 + kChunk);     // in flight while this stage is processed
     for (int t = 0; t < nt; ++t) {
       const float x = x_s[t * kCols + c], dt = dt_s[t], a = a_s[t];
       const float xdt = dt * x;
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(const vila_sel
   const float Dc = ch_ok ? p.D[ch] : 0.f;
   uint32_t rb[BCN], rc[BCN], rx[XN], rd[XN], rz[XN];     // raw bits: converted when they go to shared memory
   const int dt_in = p.in_dtype;
-  float dbias[XN];                                       // a thread stages the same channels in every round
+  float dbias[XN];                                       // a thread stages the same channels in every stage
 #pragma unroll
   for (int k = 0; k < XN; ++k) {
     const int gc = ch0 + (tid + k * kThreads) % kCols;
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(const vila_sel
       z_s[idx] = p.z ? silu_exact_f(raw_to_float(rz[k], dt_in)) : 1.0f;
     }
     __syncthreads();
-    if (t0 + kChunk < n) fetch(t0 + kChunk);     // in flight while this round is processed
+    if (t0 + kChunk < n) fetch(t0 + kChunk);     // in flight while this stage is processed
     for (int t = 0; t < nt; ++t) {
       const float x = x_s[t * kCols + c], dt = dt_s[t * kCols + c];
       const float xdt = dt * x;
