@@ -156,7 +156,7 @@ def check_logits(cfg, model, prompts, got, dtype):
 # ------------------------------------------------------------------------------------------------
 def test_embedding_with_sinusoidal_positions(cuda):
     ops = _ops()
-    for cols, scale in ((7, 0.5), (64, 1.0), (130, 2.5)):
+    for cols, scale in ((7, 0.5), (64, 1.0), (130, 2.5), (1030, 1.0)):
         table = rnd(50, cols, seed=cols).to(BF)
         ids = torch.randint(0, 50, (9,), generator=torch.Generator().manual_seed(1))
         pos = torch.tensor([0, 1, 2, 63, 64, 1000, 4097, 123457, 5])
@@ -365,7 +365,8 @@ def attend_direct(q, K, V, pos0, *, sink, scale, table, chunk, gate):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF])
-@pytest.mark.parametrize("H,G,d,chunk", [(4, 2, 12, 24), (3, 3, 20, 50), (8, 1, 32, 64), (1, 1, 8, 0), (2, 1, 5, 1), (6, 2, 16, 7)])
+@pytest.mark.parametrize("H,G,d,chunk", [(4, 2, 12, 24), (3, 3, 20, 50), (8, 1, 32, 64), (1, 1, 8, 0), (2, 1, 5, 1), (6, 2, 16, 7),
+                                         (40, 1, 16, 24), (32, 8, 64, 96)])
 def test_attention_with_distance_bias_chunks_sink_and_gate(cuda, dtype, H, G, d, chunk):
     """portions that start and end inside pages and chunks, shuffled physical pages, prompt tiles and decoded rows
     (1 / 3 key splits) in the same pool"""

@@ -94,6 +94,8 @@ struct AttnShape {
   int BQ;      // query rows per CTA
   int BK;      // keys per block (<= 32: one lane per key in the softmax step)
   int sub;     // CTAs per 16-row tile (grid.y)
+  int hsplit;  // head groups per tile (grid.z of the tiled kernel): 1 = all heads in one CTA, G = one K/V head and
+               // its query heads per CTA (possible when the heads' scores are not mixed)
 };
 
 __device__ __forceinline__ size_t pool_row(const int32_t* pt, int page, int j) {
@@ -113,12 +115,15 @@ __device__ __forceinline__ float out_gate(const vila_paged_attn_params& p, int r
 
 // K | V rows of a key block, widened to fp32: one warp per key.  16-byte loads when the head sizes allow
 // (bf16: multiples of 8, fp32: multiples of 4; the pool row is then 16-byte aligned as well).
+// g0, G: the K/V heads g0 .. g0 + G - 1 of the pool row are loaded (all of them by default).
 __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_paged_attn_params& p,
                                               const int32_t* pt, int j0, int nkeys, int BK, int D4, int DS, int V4,
-                                              int nwarps = kWarps) {
+                                              int nwarps = kWarps, int g0 = 0, int G = 0) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int G = p.G, D = p.dim, V = p.vdim, KS = key_stride(p.G, DS);
-  const size_t prw = static_cast<size_t>(G) * (D + V);
+  if (G == 0) G = p.G;
+  const int D = p.dim, V = p.vdim, KS = key_stride(G, DS);
+  const size_t prw = static_cast<size_t>(p.G) * (D + V);
+  const size_t koff = static_cast<size_t>(g0) * D, voff = static_cast<size_t>(p.G) * D + static_cast<size_t>(g0) * V;
   const bool vec16 = p.pool_dtype == VILA_DT_BF16 && (D & 7) == 0 && (V & 7) == 0;
   const bool vec32 = p.pool_dtype == VILA_DT_F32 && (D & 3) == 0 && (V & 3) == 0;
   for (int jj = warp; jj < BK; jj += nwarps) {
@@ -133,8 +138,8 @@ __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_p
     const size_t src = pool_row(pt, p.page, j) * prw;
     if (vec16) {
       const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.pool) + src;
-      const uint4* k4 = reinterpret_cast<const uint4*>(base);
-      const uint4* v4 = reinterpret_cast<const uint4*>(base + static_cast<size_t>(G) * D);
+      const uint4* k4 = reinterpret_cast<const uint4*>(base + koff);
+      const uint4* v4 = reinterpret_cast<const uint4*>(base + voff);
       for (int x = lane; x < (G * D) >> 3; x += 32) {
         const uint4 u = __ldg(k4 + x);
         const int e = x << 3, g = e / D, k = e - g * D;
@@ -154,8 +159,8 @@ __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_p
       }
     } else if (vec32) {
       const float* base = static_cast<const float*>(p.pool) + src;
-      const float4* k4 = reinterpret_cast<const float4*>(base);
-      const float4* v4 = reinterpret_cast<const float4*>(base + static_cast<size_t>(G) * D);
+      const float4* k4 = reinterpret_cast<const float4*>(base + koff);
+      const float4* v4 = reinterpret_cast<const float4*>(base + voff);
       for (int x = lane; x < (G * D) >> 2; x += 32) {
         const int e = x << 2, g = e / D, k = e - g * D;
         *reinterpret_cast<float4*>(kd + g * DS + k) = __ldg(k4 + x);
@@ -164,9 +169,9 @@ __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_p
     } else {
       for (int x = lane; x < G * D4; x += 32) {
         const int g = x / D4, k = x - g * D4;
-        kd[g * DS + k] = k < D ? ld_any(p.pool, p.pool_dtype, src + static_cast<size_t>(g) * D + k) : 0.f;
+        kd[g * DS + k] = k < D ? ld_any(p.pool, p.pool_dtype, src + koff + static_cast<size_t>(g) * D + k) : 0.f;
       }
-      const size_t vsrc = src + static_cast<size_t>(G) * D;
+      const size_t vsrc = src + voff;
       for (int x = lane; x < G * V4; x += 32) {
         const int g = x / V4, k = x - g * V4;
         vd[x] = k < V ? ld_any(p.pool, p.pool_dtype, vsrc + static_cast<size_t>(g) * V + k) : 0.f;
@@ -321,7 +326,9 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
 template <int NACC, int NT, int TR>
 __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_attn_params p, const AttnShape sh) {
   extern __shared__ __align__(16) float sm[];
-  const int H = p.H, G = p.G, D = p.dim, V = p.vdim, BQ = sh.BQ, BK = sh.BK, HK = sh.BK >> 1;
+  // H, G: the heads this CTA serves (all of them, or one K/V head with its query heads: global heads h0 + h, g0 + g)
+  const int H = p.H / sh.hsplit, G = p.G / sh.hsplit, h0 = blockIdx.z * H, g0 = blockIdx.z * G;
+  const int D = p.dim, V = p.vdim, BQ = sh.BQ, BK = sh.BK, HK = sh.BK >> 1;
   const int D4 = round4(D), DS = D4 + 4, V4 = round4(V), R = BQ * H, NB = R >> 2, rep = H / G, KS = key_stride(G, DS);
   float* Qs = sm;
   float* Ks = Qs + R * D4;
@@ -342,11 +349,11 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
 
   for (int idx = tid; idx < R * D4; idx += NT) {
     const int r = idx / D4, k = idx - r * D4, h = r / BQ, i = r - h * BQ;
-    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * H + h) * D + k] * p.scale : 0.f;
+    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * p.H + h0 + h) * D + k] * p.scale : 0.f;
   }
   for (int idx = tid; idx < H * H; idx += NT) Tk[idx] = p.talk ? p.talk[idx] : ((idx / H) == (idx % H) ? 1.f : 0.f);
   for (int r = tid; r < R; r += NT) {
-    m_s[r] = p.sink ? p.sink[r / BQ] : kNegBig;
+    m_s[r] = p.sink ? p.sink[h0 + r / BQ] : kNegBig;
     l_s[r] = p.sink ? 1.0f : 0.0f;
   }
   float4 acc[NACC][4];
@@ -361,7 +368,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
 
   for (int j0 = (first_key(p, pos0) / BK) * BK; j0 < nkeys; j0 += BK) {
     __syncthreads();
-    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, NT / 32);
+    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, NT / 32, g0, G);
     __syncthreads();
     for (int item = tid; item < (R / TR) * HK; item += NT) {
       const int rbs = item / HK, jp = item - rbs * HK, r0 = rbs * TR;     // TR score rows of one head x 2 keys
@@ -415,7 +422,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
               s1 = fmaf(tk[g + 1], sr[(g + 1) * BQ * BK], s1);
             }
             if (g < H) s0 = fmaf(tk[g], sr[g * BQ * BK], s0);
-            if (ok[u]) sv[u] = s0 + s1 + (p.dist_bias ? dist_bias(p, pos0 + i - (j0 + lane), h) : 0.f);
+            if (ok[u]) sv[u] = s0 + s1 + (p.dist_bias ? dist_bias(p, pos0 + i - (j0 + lane), h0 + h) : 0.f);
           }
           mo[u] = m_s[r];
         }
@@ -489,9 +496,9 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
     for (int k = 0; k < 4; ++k) {
       const int r = (rb << 2) + k, h = r / BQ, i = r - h * BQ;
       if (i >= n) continue;
-      const float inv = out_gate(p, row0 + i, h) / l_s[r];
+      const float inv = out_gate(p, row0 + i, h0 + h) / l_s[r];
       const float v[4] = {acc[a][k].x, acc[a][k].y, acc[a][k].z, acc[a][k].w};
-      const size_t ob = (static_cast<size_t>(row0 + i) * H + h) * V + 4 * c4;
+      const size_t ob = (static_cast<size_t>(row0 + i) * p.H + h0 + h) * V + 4 * c4;
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         if (4 * c4 + e < V) st_any(p.out, p.out_dtype, ob + e, v[e] * inv);
@@ -517,10 +524,11 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const vila_paged_
   }
 }
 
-size_t attn_smem(const vila_paged_attn_params& p, int BQ, int BK) {
-  const int D4 = round4(p.dim), V4 = round4(p.vdim), R = BQ * p.H;
-  return sizeof(float) * (static_cast<size_t>(R) * D4 + static_cast<size_t>(BK) * key_stride(p.G, D4 + 4) +
-                          static_cast<size_t>(BK) * p.G * V4 + 2 * static_cast<size_t>(R) * BK + p.H * p.H + 3 * R);
+size_t attn_smem(const vila_paged_attn_params& p, int BQ, int BK, int H = 0, int G = 0) {
+  if (H == 0) { H = p.H; G = p.G; }
+  const int D4 = round4(p.dim), V4 = round4(p.vdim), R = BQ * H;
+  return sizeof(float) * (static_cast<size_t>(R) * D4 + static_cast<size_t>(BK) * key_stride(G, D4 + 4) +
+                          static_cast<size_t>(BK) * G * V4 + 2 * static_cast<size_t>(R) * BK + H * H + 3 * R);
 }
 
 }  // namespace
@@ -546,20 +554,24 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
   VB_CHECK(p.max_rows >= 1 && p.max_rows <= 16 && (p.nsplit == 1 || p.max_rows == 1),
            "paged_attention: max_rows=%d nsplit=%d (key splitting serves one-row tiles)", p.max_rows, p.nsplit);
   AttnShape sh;
-  if (p.max_rows > 1 && p.H <= 32) {
+  // Without head mixing the K/V-head groups are independent: a CTA then serves ONE K/V head and its query heads, holds
+  // a quarter .. an eighth of the K | V block, and takes more rows of the sequence instead.
+  sh.hsplit = (p.talk == nullptr && p.max_rows > 1) ? p.G : 1;
+  const int Hl = p.H / sh.hsplit, Gl = p.G / sh.hsplit;
+  if (p.max_rows > 1 && Hl <= 32) {
     // prompt portions: the register-tiled kernel, 4 .. 16 rows per CTA (about 64 score rows, 128 at most)
     sh.BQ = 16;
-    while (sh.BQ > 4 && sh.BQ * p.H > 64) sh.BQ >>= 1;
+    while (sh.BQ > 4 && sh.BQ * Hl > 64) sh.BQ >>= 1;
     sh.BK = 32;
-    while (attn_smem(p, sh.BQ, sh.BK) > kSmemMax && sh.BK > 8) sh.BK >>= 1;
-    const size_t smem4 = attn_smem(p, sh.BQ, sh.BK);
-    const int items = (sh.BQ * p.H / 4) * (round4(p.vdim) >> 2);      // accumulator items (4 rows x 4 columns)
+    while (attn_smem(p, sh.BQ, sh.BK, Hl, Gl) > kSmemMax && sh.BK > 8) sh.BK >>= 1;
+    const size_t smem4 = attn_smem(p, sh.BQ, sh.BK, Hl, Gl);
+    const int items = (sh.BQ * Hl / 4) * (round4(p.vdim) >> 2);      // accumulator items (4 rows x 4 columns)
     // 512 threads (16 warps on the SM, 2-row score tiles) when there is accumulator work for them
     const int nt = items >= 512 ? 512 : 256;
     const int nacc4 = (items + nt - 1) / nt;
     if (smem4 <= kSmemMax && nacc4 <= (nt == 512 ? 2 : 4)) {
       sh.sub = (p.max_rows + sh.BQ - 1) / sh.BQ;
-      const dim3 grid4(p.ntiles, sh.sub, 1);
+      const dim3 grid4(p.ntiles, sh.sub, sh.hsplit);
 #define VB_PAGED4(N, NT, TR)                                                                                     \
   do {                                                                                                           \
     if (smem4 > 48 * 1024)                                                                                       \
@@ -578,6 +590,7 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
     }
   }
   // decoded tokens (one-row tiles, keys optionally split over CTAs) and shapes the tiled kernel does not take
+  sh.hsplit = 1;
   sh.BQ = 1;
   while (sh.BQ < p.max_rows) sh.BQ <<= 1;
   while (sh.BQ > 1 && sh.BQ * p.H > 64) sh.BQ >>= 1;

@@ -355,18 +355,20 @@ inline int flat_grid(size_t total) {
 }
 
 // ---- scaled embedding + sinusoidal positions ---------------------------------------------------------
-// A warp per row; a lane takes column pairs (2i, 2i + 1) = (sin, cos) of ONE angle position * inv_freq[i].
+// A warp (narrow rows) or a CTA (wide rows) per row; a thread takes column pairs (2i, 2i + 1) = (sin, cos) of ONE
+// angle position * inv_freq[i].
 // The angle is formed and brought into [-pi, pi] in double, so that far positions keep their phase (an fp32
 // product loses it); sine and cosine of the reduced angle are evaluated in fp32.
+template <int TPR>
 __global__ void __launch_bounds__(kRowThreads)
 embed_sincos_rows_kernel(const void* __restrict__ table, int dt, const int32_t* __restrict__ ids,
                          const int32_t* __restrict__ positions, const double* __restrict__ inv_freq, float scale,
                          float* __restrict__ out, void* __restrict__ copy, int c_dt, int rows, int cols) {
-  const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+  const int row = row_of<TPR>();
   if (row >= rows) return;
   const size_t src = static_cast<size_t>(ids[row]) * cols, dst = static_cast<size_t>(row) * cols;
   const double pos = static_cast<double>(positions[row]);
-  for (int i = lane_id(); 2 * i < cols; i += 32) {
+  for (int i = col0_of<TPR>(); 2 * i < cols; i += TPR) {
     const double ang = pos * inv_freq[i];
     const float red = static_cast<float>(fma(-6.283185307179586476925, rint(ang * 0.15915494309189533577), ang));
     float sn, cs;
@@ -533,8 +535,12 @@ int embed_sincos_rows(const void* table, int dt, const int32_t* ids, const int32
                       float scale, float* out, void* copy, int c_dt, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0) return 0;
   VB_CHECK(cols >= 1 && inv_freq != nullptr && positions != nullptr, "embed_sincos_rows: cols=%d", cols);
-  VB_CUDA(launch_serial(embed_sincos_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, table, dt, ids,
-                        positions, inv_freq, scale, out, copy, c_dt, rows, cols));
+  if (cols >= kWideCols)
+    VB_CUDA(launch_serial(embed_sincos_rows_kernel<256>, dim3(rows), dim3(kRowThreads), 0, stream, table, dt, ids,
+                          positions, inv_freq, scale, out, copy, c_dt, rows, cols));
+  else
+    VB_CUDA(launch_serial(embed_sincos_rows_kernel<32>, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, table, dt,
+                          ids, positions, inv_freq, scale, out, copy, c_dt, rows, cols));
   return 0;
 }
 
