@@ -1546,7 +1546,7 @@ def ssm_lm_block(args, peaks):
         t = timed_op(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, **akw, **okw))
         led["paged_attention prefill, chunk %d + distance bias + gate" % ck] = rate(t, flop=H * pairs_chunk * 4.0 * 128)
         t = timed_op(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, **akw))
-        led["paged_attention prefill, plain causal (the kernel as the rotary GQA model uses it)"] = rate(
+        led["paged_attention prefill, plain causal, heads not mixed"] = rate(
             t, flop=H * (S * (S + 1) / 2) * 4.0 * 128)
         kvb = torch.randn(S, H * 256, device=dev).to(bf)
         qb = torch.randn(S, H * 128, device=dev).to(bf)
