@@ -366,7 +366,7 @@ def attend_direct(q, K, V, pos0, *, sink, scale, table, chunk, gate):
 
 @pytest.mark.parametrize("dtype", [F32, BF])
 @pytest.mark.parametrize("H,G,d,chunk", [(4, 2, 12, 24), (3, 3, 20, 50), (8, 1, 32, 64), (1, 1, 8, 0), (2, 1, 5, 1), (6, 2, 16, 7),
-                                         (40, 1, 16, 24), (32, 8, 64, 96)])
+                                         (40, 1, 16, 24), (32, 8, 64, 80)])
 def test_attention_with_distance_bias_chunks_sink_and_gate(cuda, dtype, H, G, d, chunk):
     """portions that start and end inside pages and chunks, shuffled physical pages, prompt tiles and decoded rows
     (1 / 3 key splits) in the same pool"""
@@ -421,12 +421,12 @@ def test_chunk_edges_far_keys_and_the_sink_show(cuda, decode):
         keys[j, 0] = big
         return keys, (big * (60.0 / 16.0)).expand(n, H, d).contiguous()
 
-    # the chunk of the last rows starts at 672 (chunk 96) -> key 672 inside, key 671 outside
+    # the chunk of the last rows starts at 672 (chunk 112) -> key 672 inside, key 671 outside
     keys, q = standing_out(672)
-    assert rel(run(q, 96, keys), V[672, 0].expand(n, H, d)) < 1e-4
+    assert rel(run(q, 112, keys), V[672, 0].expand(n, H, d)) < 1e-4
     keys, q = standing_out(671)
-    out = run(q, 96, keys)
-    want = attend_direct(q, keys, V, pos0, sink=None, scale=1.0, table=None, chunk=96, gate=None)
+    out = run(q, 112, keys)
+    want = attend_direct(q, keys, V, pos0, sink=None, scale=1.0, table=None, chunk=112, gate=None)
     assert rel(out, want) < 1e-4 and rel(out, V[671, 0].expand(n, H, d)) > 0.1
     # a far key with one long chunk, and without chunks
     keys, q = standing_out(13)
