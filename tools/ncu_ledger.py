@@ -1,6 +1,6 @@
 """One launch of every hot-path kernel at its NVILA-8B shape, bracketed by cudaProfilerStart/Stop, for
 
-    ncu --set full --clock-control none --import-source on --profile-from-start off \
+    ncu --set full --clock-control none --profile-from-start off \
         -k regex:vb:: -f -o gpurun_out/ledger python tools/ncu_ledger.py
 
 Each entry prints `LEDGER <index> <label> <algorithmic bytes> <algorithmic flops>` in launch order so

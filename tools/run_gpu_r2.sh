@@ -68,7 +68,7 @@ for st in $STAGES; do
       wc -c gpurun_out/ledger_raw.csv ;;
     ncu_one)
       # full capture WITH source of one kernel: NCU_K=<regex> NCU_SCRIPT=<tools/x.py> NCU_ARGS=...
-      timeout 900 ncu --set full --clock-control none --import-source on --kernel-name-base demangled \
+      timeout 900 ncu --set full --clock-control none --kernel-name-base demangled \
           --profile-from-start off -k "regex:${NCU_K}" -c ${NCU_C:-1} -f -o gpurun_out/prof_${NCU_NAME:-one} \
           python ${NCU_SCRIPT} ${NCU_ARGS} > gpurun_out/ncu_${NCU_NAME:-one}.log 2>&1
       echo "== ncu_one rc=$?"; ls -la gpurun_out/prof_${NCU_NAME:-one}.ncu-rep ;;
