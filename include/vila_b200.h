@@ -70,6 +70,9 @@ int vila_device_info(int* sm_count, int* cc_major, int* cc_minor);
 int vila_linear(const void* x, int64_t ldx, const void* w, int64_t ldw, const void* bias,
                 const void* residual, int64_t ld_res, int res_row_mod, void* out, int64_t ldo,
                 int M, int N, int K, int act, int flags, void* stream);
+/* vila_linear with the coefficients of a two-parameter activation (VILA_ACT_XIELU: act_pos, act_neg); no residual. */
+int vila_linear_act(const void* x, int64_t ldx, const void* w, int64_t ldw, const void* bias, void* out, int64_t ldo,
+                    int M, int N, int K, int act, float act_pos, float act_neg, int flags, void* stream);
 /* test hook: same, forcing the kernel configuration instead of the size heuristic:
  *   64 / 128 / 256   single-CTA tiles 128 x block_n (+1000: deterministic stream-K, +2000: stream-K off)
  *   4128 / 4256      CTA-pair tiles 256 x {128,256} (tcgen05 cta_group::2)
@@ -380,8 +383,34 @@ typedef struct vila_latent_attn_params {
   int32_t cache_dtype, gate_dtype, out_dtype;
   int32_t ntiles, pt_stride, H, R, page, decode, nsplit;
   float scale;
+  int32_t window; /* > 0: row i sees the keys pos(i) - window < j <= pos(i) only; 0: all keys up to pos(i) */
 } vila_latent_attn_params;
 int vila_latent_attention(const vila_latent_attn_params* p, void* stream);
+
+/* vila_latent_rope_append — what a latent-attention layer with a decoupled rotary part does between its
+ * projections and vila_latent_attention (all fp32 arithmetic, angles in double):
+ *   kv != NULL: pool row cache_rows[t] = rmsnorm(kv[t, :R]) * norm_w | rotate(kv[t, R : R + rot])
+ *               (the normed latent and ONE rotated key part shared by all heads)
+ *   q  != NULL: qa[t, h, R : R + rot] = rotate(q[t, h, q_off : q_off + rot])  for every head h, where
+ *               head h of q starts at column h * q_head; qa rows are H * (R + rot) wide and their
+ *               first R columns per head (the query with the key expansion folded in) are left alone.
+ * rotate turns the pairs (2i, 2i+1) (layout 0) or (i, i + rot / 2) (layout 1) by positions[t] *
+ * inv_freq[i] (fp64 [rot / 2]) and multiplies cos and sin by mscale. */
+typedef struct vila_latent_rope_params {
+  const void* kv; /* [T, ld_kv] or NULL */
+  int64_t ld_kv;
+  const float* norm_w; /* [R] or NULL */
+  void* pool;          /* [pool rows, R + rot] */
+  const int32_t* cache_rows;
+  const void* q; /* [T, ld_q] or NULL */
+  int64_t ld_q;
+  float* qa; /* [T, H * (R + rot)] */
+  const int32_t* positions;
+  const double* inv_freq;
+  int32_t kv_dtype, pool_dtype, q_dtype, T, H, R, rot, q_head, q_off, layout;
+  float eps, mscale;
+} vila_latent_rope_params;
+int vila_latent_rope_append(const vila_latent_rope_params* p, void* stream);
 
 /* vila_hgrn2_scan — gated linear recurrence with the forget gate tied to the input gate, per head:
  *   q_t = silu(zq_t),  f_t = lower + (1 - lower) * sigmoid(zf_t + f_bias)
@@ -445,8 +474,15 @@ int vila_sink_attention(const vila_sink_attn_params* p, void* stream);
  *   g = min(z_gate, act_limit), u = clamp(z_up, -act_limit, act_limit), out = g * sigmoid(act_alpha * g) * (u + 1)
  * act_alpha / act_limit travel in vila_glinear_ext, passed through vila_glinear_x. */
 #define VILA_FLAG_GLU_CLAMP 4
+/* act = VILA_ACT_XIELU: z > 0: act_pos z^2 + z / 2;  z <= 0: act_neg (e^z - 1 - z) + z / 2
+ * in_scale (fp32, may be NULL; o_rows must be NULL then): the accumulators of sorted position i are
+ *   multiplied by in_scale[a_rows ? a_rows[i] : i] BEFORE bias and activation, which is the layer applied
+ *   to the scaled input row (a routing weight on an expert's input rather than on its output). */
+#define VILA_ACT_XIELU 5
 typedef struct vila_glinear_ext {
   float act_alpha, act_limit;
+  float act_pos, act_neg;
+  const float* in_scale;
 } vila_glinear_ext;
 int vila_glinear_x(const vila_glinear_params* p, const vila_glinear_ext* x, void* stream);
 
@@ -500,6 +536,8 @@ typedef struct vila_rope_append_params {
   const float* q_norm_w; /* [dim] or NULL */
   const float* k_norm_w; /* [dim] or NULL */
   int32_t v_from_k;
+  int32_t rot_layout; /* 0: pairs (2i, 2i+1); 1: pairs (i, i + rot_dims / 2) */
+  float rot_mscale;   /* cos and sin are multiplied by this; 0 counts as 1 */
 } vila_rope_append_params;
 int vila_rope_append(const vila_rope_append_params* p, void* stream);
 
@@ -531,6 +569,14 @@ typedef struct vila_paged_attn_params {
   const void* gate;       /* [T, ldg] pre-activations, column h = head h, or NULL */
   int64_t ldg;
   int32_t dist_rows, chunk, gate_dtype;
+  /* window > 0: a key is seen only if pos(i) - j < window or j < keep_first (the first keep_first tokens
+   * of a sequence stay visible, at their true positions); window == 0: no such limit.
+   * talk_after != 0: talk mixes the heads' softmax WEIGHTS instead of their scores,
+   *   p_h(i, j) <- sum_g talk[h, g] p_g(i, j), head h then sums the values of its own K/V head; the
+   *   kernel makes two passes over the keys (running max and sum of every head first); no sink then.
+   * head_scale fp32 [H] or NULL: the scores of head h are multiplied by head_scale[h] (before mixing). */
+  int32_t window, keep_first, talk_after;
+  const float* head_scale;
 } vila_paged_attn_params;
 int vila_paged_attention(const vila_paged_attn_params* p, void* stream);
 
@@ -548,6 +594,13 @@ int vila_moe_route_sigmoid(const void* x, int x_dtype, int64_t ldx, const float*
 int vila_residual_add_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part,
                            int part_dtype, int64_t ldp, int n_partials, float mult, void* copy,
                            int copy_dtype, int rows, int cols, void* stream);
+
+/* Pre-norm residual step in one pass: x[r, :] += a[r, :] + sum_{j < n_partials} part[r * n_partials + j, :] (a or
+ * part may be NULL), then out[r, :] = x[r, :] / sqrt(mean(x[r, :]^2) + eps) * w (w may be NULL): the updated stream
+ * and the normed operand of the next sublayer.  out is [rows, cols] contiguous in out_dtype. */
+int vila_residual_norm_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part, int part_dtype,
+                            int64_t ldp, int n_partials, const void* w, int w_dtype, float eps, void* out,
+                            int out_dtype, int rows, int cols, void* stream);
 
 /* Group RMS norm + causal short convolution for up to two sublayers that read the same rows x, in one
  * pass (vila_group_rmsnorm_rows followed by vila_short_conv_rows / vila_short_conv_state per sublayer):

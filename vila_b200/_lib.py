@@ -89,6 +89,17 @@ class LatentAttnParams(C.Structure):
         ("cache_dtype", C.c_int32), ("gate_dtype", C.c_int32), ("out_dtype", C.c_int32),
         ("ntiles", C.c_int32), ("pt_stride", C.c_int32), ("H", C.c_int32), ("R", C.c_int32),
         ("page", C.c_int32), ("decode", C.c_int32), ("nsplit", C.c_int32), ("scale", c_float),
+        ("window", C.c_int32),
+    ]
+
+
+class LatentRopeParams(C.Structure):
+    _fields_ = [
+        ("kv", c_void_p), ("ld_kv", c_i64), ("norm_w", c_void_p), ("pool", c_void_p), ("cache_rows", c_void_p),
+        ("q", c_void_p), ("ld_q", c_i64), ("qa", c_void_p), ("positions", c_void_p), ("inv_freq", c_void_p),
+        ("kv_dtype", C.c_int32), ("pool_dtype", C.c_int32), ("q_dtype", C.c_int32), ("T", C.c_int32),
+        ("H", C.c_int32), ("R", C.c_int32), ("rot", C.c_int32), ("q_head", C.c_int32), ("q_off", C.c_int32),
+        ("layout", C.c_int32), ("eps", c_float), ("mscale", c_float),
     ]
 
 
@@ -112,7 +123,8 @@ class Hgrn2Params(C.Structure):
 
 
 class GLinearExt(C.Structure):
-    _fields_ = [("act_alpha", c_float), ("act_limit", c_float)]
+    _fields_ = [("act_alpha", c_float), ("act_limit", c_float), ("act_pos", c_float), ("act_neg", c_float),
+                ("in_scale", c_void_p)]
 
 
 class RopeAppendParams(C.Structure):
@@ -123,6 +135,7 @@ class RopeAppendParams(C.Structure):
         ("G", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("rot_dims", C.c_int32),
         ("unit_norm", C.c_int32), ("eps", c_float),
         ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("v_from_k", C.c_int32),
+        ("rot_layout", C.c_int32), ("rot_mscale", c_float),
     ]
 
 
@@ -135,6 +148,7 @@ class PagedAttnParams(C.Structure):
         ("nsplit", C.c_int32), ("max_rows", C.c_int32), ("scale", c_float),
         ("dist_bias", c_void_p), ("gate", c_void_p), ("ldg", c_i64),
         ("dist_rows", C.c_int32), ("chunk", C.c_int32), ("gate_dtype", C.c_int32),
+        ("window", C.c_int32), ("keep_first", C.c_int32), ("talk_after", C.c_int32), ("head_scale", c_void_p),
     ]
 
 
@@ -183,6 +197,8 @@ SIGNATURES = {
     "vila_set_workspace": [c_void_p, C.c_uint64],
     "vila_linear": [c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_int, c_void_p,
                     c_i64, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "vila_linear_act": [c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_int, c_int, c_int, c_int,
+                        c_float, c_float, c_int, c_void_p],
     "vila_linear_cfg": [c_int, c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p, c_i64, c_int,
                         c_void_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "vila_layernorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -220,6 +236,7 @@ SIGNATURES = {
                                  c_int, c_void_p, c_int, c_float, c_float, c_int, c_int, c_void_p],
     "vila_glinear": [C.POINTER(GLinearParams), c_void_p],
     "vila_latent_attention": [C.POINTER(LatentAttnParams), c_void_p],
+    "vila_latent_rope_append": [C.POINTER(LatentRopeParams), c_void_p],
     "vila_hgrn2_scan": [C.POINTER(Hgrn2Params), c_void_p],
     "vila_sink_attention": [C.POINTER(SinkAttnParams), c_void_p],
     "vila_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -241,6 +258,8 @@ SIGNATURES = {
                                c_int, c_int, c_int, c_void_p],
     "vila_residual_add_rows": [c_void_p, c_void_p, c_int, c_i64, c_void_p, c_int, c_i64, c_int, c_float, c_void_p,
                                c_int, c_int, c_int, c_void_p],
+    "vila_residual_norm_rows": [c_void_p, c_void_p, c_int, c_i64, c_void_p, c_int, c_i64, c_int, c_void_p, c_int,
+                                c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "vila_norm_conv_rows": [C.POINTER(NormConvParams), c_void_p],
     "vila_gated_norm_residual_scaled": [c_void_p, c_void_p, c_int, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p,
                                         c_int, c_void_p, c_int, c_float, c_float, c_float, c_int, c_int, c_void_p],

@@ -76,6 +76,15 @@ int vila_linear(const void* x, int64_t ldx, const void* w, int64_t ldw, const vo
                        make_epi(bias, residual, ld_res, res_row_mod, act, swiglu), st(stream));
 }
 
+int vila_linear_act(const void* x, int64_t ldx, const void* w, int64_t ldw, const void* bias, void* out, int64_t ldo,
+                    int M, int N, int K, int act, float act_pos, float act_neg, int flags, void* stream) {
+  VB_REQUIRE_DEVICE();
+  vb::GemmEpilogue e = make_epi(bias, nullptr, 0, 0, act, flags);
+  e.act_pos = act_pos;
+  e.act_neg = act_neg;
+  return vb::gemm_bf16(cb(x), (int)ldx, cb(w), (int)ldw, mb(out), (int)ldo, M, N, K, e, st(stream));
+}
+
 int vila_linear_cfg(int block_n, const void* x, int64_t ldx, const void* w, int64_t ldw,
                     const void* bias, const void* residual, int64_t ld_res, int res_row_mod,
                     void* out, int64_t ldo, int M, int N, int K, int act, int swiglu, void* stream) {
@@ -360,6 +369,11 @@ int vila_latent_attention(const vila_latent_attn_params* p, void* stream) {
   return vb::latent_attention(*p, st(stream));
 }
 
+int vila_latent_rope_append(const vila_latent_rope_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::latent_rope_append(*p, st(stream));
+}
+
 int vila_sink_attention(const vila_sink_attn_params* p, void* stream) {
   VB_REQUIRE_DEVICE();
   return vb::sink_attention(*p, st(stream));
@@ -443,6 +457,14 @@ int vila_moe_route_sigmoid(const void* x, int x_dtype, int64_t ldx, const float*
   VB_REQUIRE_DEVICE();
   return vb::moe_route_sigmoid(x, x_dtype, ldx, w_router, correction, idx, weight, rows, cols, experts, top,
                                groups, keep, st(stream));
+}
+
+int vila_residual_norm_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part, int part_dtype,
+                            int64_t ldp, int n_partials, const void* w, int w_dtype, float eps, void* out,
+                            int out_dtype, int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::residual_norm_rows(x, a, a_dtype, lda, part, part_dtype, ldp, n_partials, w, w_dtype, eps, out, out_dtype,
+                                rows, cols, st(stream));
 }
 
 int vila_residual_add_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part,

@@ -77,6 +77,10 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float t = 1.0f - __fdividef(2.0f, __expf(2.0f * u) + 1.0f);
   return 0.5f * x * (1.0f + t);
 }
+// z > 0: a_pos z^2 + z / 2;  z <= 0: a_neg (e^z - 1 - z) + z / 2   (a_pos, a_neg > 0 come ready-made)
+__device__ __forceinline__ float xielu_f(float z, float a_pos, float a_neg) {
+  return z > 0.f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+}
 __device__ __forceinline__ float gelu_erf_f(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
 }

@@ -467,7 +467,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               v[j] = epi.act == ACT_GELU_TANH
                          ? gelu_tanh_f(x)
                          : (epi.act == ACT_GELU_ERF ? gelu_erf_f(x)
-                                                    : (epi.act == ACT_RELU2 ? fmaxf(x, 0.f) * fmaxf(x, 0.f) : silu_f(x)));
+                                                    : (epi.act == ACT_RELU2 ? fmaxf(x, 0.f) * fmaxf(x, 0.f)
+                                                       : (epi.act == ACT_XIELU ? xielu_f(x, epi.act_pos, epi.act_neg) : silu_f(x))));
             }
           }
           if (row_ok) {

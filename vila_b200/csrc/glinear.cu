@@ -24,6 +24,11 @@ __device__ __forceinline__ float glu_clamp_f(float zg, float zu, const vila_glin
   return g * sigmoid_f(x.act_alpha * g) * (u + 1.0f);
 }
 
+// scale of the INPUT row behind sorted position i (= output row: in_scale is only taken without o_rows)
+__device__ __forceinline__ float in_scale_of(const vila_glinear_params& p, const vila_glinear_ext& x, int i) {
+  return x.in_scale ? x.in_scale[p.a_rows ? p.a_rows[i] : i] : 1.0f;
+}
+
 // Epilogue of a thread's TM x 4 block: bias, activation (or SwiGLU over column pairs), routing weight,
 // scatter through the output row index.
 template <int TM>
@@ -37,17 +42,18 @@ __device__ __forceinline__ void store_block(const vila_glinear_params& p, const 
     const int orow = orows[i];
     if (orow < 0) continue;
     const float rs = p.row_scale ? p.row_scale[orow] : 1.0f;
+    const float is = in_scale_of(p, x, orow);
     float v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      float z = acc[i][j];
+      float z = acc[i][j] * is;
       if (p.bias && n < p.N) z += ld_any(p.bias, p.w_dtype, static_cast<size_t>(g) * p.bias_group_stride + n);
       if (p.act == VILA_ACT_SILU) z = silu_exact_f(z);
       else if (p.act == VILA_ACT_RELU2) { z = fmaxf(z, 0.f); z = z * z; }
       else if (p.act == VILA_ACT_GELU_TANH) {
         z = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-      }
+      } else if (p.act == VILA_ACT_XIELU) z = xielu_f(z, x.act_pos, x.act_neg);
       v[j] = z;
     }
     const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
@@ -261,12 +267,13 @@ __device__ __forceinline__ void load8(const void* p, int dt, size_t i, float (&v
   }
 }
 
-__device__ __forceinline__ float finish(const vila_glinear_params& p, float z, int g, int n) {
+__device__ __forceinline__ float finish(const vila_glinear_params& p, const vila_glinear_ext& x, float z, int g, int n) {
   if (p.bias) z += ld_any(p.bias, p.w_dtype, static_cast<size_t>(g) * p.bias_group_stride + n);
   if (p.act == VILA_ACT_SILU) z = silu_exact_f(z);
   else if (p.act == VILA_ACT_RELU2) { z = fmaxf(z, 0.f); z = z * z; }
   else if (p.act == VILA_ACT_GELU_TANH)
     z = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  else if (p.act == VILA_ACT_XIELU) z = xielu_f(z, x.act_pos, x.act_neg);
   return z;
 }
 
@@ -338,18 +345,19 @@ __global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const v
 #pragma unroll
     for (int r = 0; r < kSmallRows; ++r) {
       if (r < nr) {   // nr is uniform over the CTA
-        const float za = warp_sum(acc_a[r]), zb = warp_sum(acc_b[r]);
         const int orow = orow_s[r];
+        const float is = in_scale_of(p, x, orow);
+        const float za = warp_sum(acc_a[r]) * is, zb = warp_sum(acc_b[r]) * is;
         if (lane == 0 && has_a) {
           const float rs = p.row_scale ? p.row_scale[orow] : 1.0f;
           const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
           if (glu_clamp) {
-            if (has_b) st_any(p.out, p.out_dtype, ob + n_a / 2, glu_clamp_f(finish(p, za, g, n_a), finish(p, zb, g, n_b), x) * rs);
+            if (has_b) st_any(p.out, p.out_dtype, ob + n_a / 2, glu_clamp_f(finish(p, x, za, g, n_a), finish(p, x, zb, g, n_b), x) * rs);
           } else if (swiglu) {
-            if (has_b) st_any(p.out, p.out_dtype, ob + n_a / 2, silu_exact_f(finish(p, za, g, n_a)) * finish(p, zb, g, n_b) * rs);
+            if (has_b) st_any(p.out, p.out_dtype, ob + n_a / 2, silu_exact_f(finish(p, x, za, g, n_a)) * finish(p, x, zb, g, n_b) * rs);
           } else {
-            st_any(p.out, p.out_dtype, ob + n_a, finish(p, za, g, n_a) * rs);
-            if (has_b) st_any(p.out, p.out_dtype, ob + n_b, finish(p, zb, g, n_b) * rs);
+            st_any(p.out, p.out_dtype, ob + n_a, finish(p, x, za, g, n_a) * rs);
+            if (has_b) st_any(p.out, p.out_dtype, ob + n_b, finish(p, x, zb, g, n_b) * rs);
           }
         }
       }
@@ -360,8 +368,9 @@ __global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const v
 }  // namespace
 
 int glinear(const vila_glinear_params& p, cudaStream_t stream, const vila_glinear_ext* ext) {
-  vila_glinear_ext x = {1.0f, INFINITY};
+  vila_glinear_ext x = {1.0f, INFINITY, 0.f, 0.f, nullptr};
   if (ext) x = *ext;
+  VB_CHECK(x.in_scale == nullptr || p.o_rows == nullptr, "glinear: in_scale is indexed through a_rows; o_rows must be NULL");
   if (p.M <= 0 || p.N <= 0) return 0;
   VB_CHECK(p.K > 0 && p.groups >= 1, "glinear: K=%d groups=%d", p.K, p.groups);
   VB_CHECK(p.mode == 0 || (p.mode == 1 && p.seg != nullptr), "glinear: mode %d needs seg", p.mode);

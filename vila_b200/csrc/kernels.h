@@ -7,7 +7,7 @@
 
 namespace vb {
 
-enum Act : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2, ACT_SILU = 3, ACT_RELU2 = 4 };
+enum Act : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2, ACT_SILU = 3, ACT_RELU2 = 4, ACT_XIELU = 5 };
 
 struct GemmEpilogue {
   const __nv_bfloat16* bias = nullptr;      // [N]
@@ -15,6 +15,7 @@ struct GemmEpilogue {
   int ld_res = 0;
   int res_row_mod = 0;
   int act = ACT_NONE;
+  float act_pos = 0.f, act_neg = 0.f;  // ACT_XIELU: z > 0: act_pos z^2 + z / 2, else act_neg (e^z - 1 - z) + z / 2
   int swiglu = 0;  // interleaved (gate, up) columns -> N/2 outputs of silu(gate) * up
   int static_w = 0;  // W is a parameter: its first pipeline stages may be fetched before the PDL wait
   // split-K (set by the launcher): fp32 partial-sum workspace [M, N] (zeroed, self-cleaning) and
@@ -238,6 +239,8 @@ int embed_pair_rows(const void* table, int dt, const void* pair, int pdt, const 
 int add_row_vector(float* x, const void* vec, int dt, int rows, int cols, cudaStream_t stream);
 int residual_add_rows(float* x, const void* a, int a_dt, int64_t lda, const void* part, int p_dt, int64_t ldp,
                       int np, float mult, void* copy, int c_dt, int rows, int cols, cudaStream_t stream);
+int residual_norm_rows(float* x, const void* a, int a_dt, int64_t lda, const void* part, int p_dt, int64_t ldp, int np,
+                       const void* w, int w_dt, float eps, void* out, int o_dt, int rows, int cols, cudaStream_t stream);
 int gelu_mul_gather(const void* z, int z_dt, const void* table, int dt, int64_t ldt, const int32_t* ids, int col0,
                     void* out, int o_dt, int rows, int cols, cudaStream_t stream);
 int moe_route_sigmoid(const void* x, int x_dt, int64_t ldx, const float* wr, const float* corr, int32_t* idx,
@@ -263,6 +266,7 @@ struct vila_latent_attn_params;
 struct vila_hgrn2_params;
 struct vila_sink_attn_params;
 struct vila_glinear_ext;
+struct vila_latent_rope_params;
 struct vila_rope_append_params;
 struct vila_paged_attn_params;
 struct vila_norm_conv_params;
@@ -281,6 +285,7 @@ int sink_attention(const vila_sink_attn_params& p, cudaStream_t stream);
 int gather_rows(const void* src, const int32_t* rows, void* dst, int n_rows, int row_bytes, cudaStream_t stream);
 int glinear(const vila_glinear_params& p, cudaStream_t stream, const vila_glinear_ext* ext = nullptr);
 int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream);
+int latent_rope_append(const vila_latent_rope_params& p, cudaStream_t stream);
 int hgrn2_scan(const vila_hgrn2_params& p, cudaStream_t stream);
 
 }  // namespace vb

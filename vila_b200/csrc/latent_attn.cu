@@ -11,6 +11,11 @@
 //   latent_attn_decode_kernel one (token, head) per CTA, all 256 threads spread over keys (decoded
 //                             tokens of models with fewer than 4 heads)
 //   both decode forms deal the key blocks of a row to nsplit CTAs; latent_attn_merge_kernel merges them
+//   window > 0: a query sees the last `window` keys up to itself only (mask + a later start of the key loop)
+// A decoupled rotary part rides in the same rows: the cache row is latent | ONE rotated key part shared by all
+// heads, the folded query of head h is (W_uk,h^T q_h | rotated q part), so the dot product over the row is the
+// sum of both score terms; the columns of the weighted sum that belong to the rotary part are simply not used by
+// the value expansion.  latent_rope_kernel writes those rows and query parts.
 #include "../../include/vila_b200.h"
 #include "common.cuh"
 #include "kernels.h"
@@ -113,7 +118,10 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
   for (int kk = 0; kk < KK4; ++kk) acc[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
   const int nkeys = kHeadRows ? pos0 + 1 : pos0 + n;
   const int my_last = kHeadRows ? pos0 : pos0 + i;  // last visible key of query i
-  for (int j0 = split * BKEY; j0 < nkeys; j0 += nsplit * BKEY) {
+  // sliding window: the first visible key of query i; the key loop starts at the block of the tile's first row
+  const int my_first = p.window > 0 ? max(my_last - p.window + 1, 0) : 0;
+  const int j_begin = p.window > 0 ? (max(pos0 - p.window + 1, 0) / BKEY) * BKEY : 0;
+  for (int j0 = j_begin + split * BKEY; j0 < nkeys; j0 += nsplit * BKEY) {
     __syncthreads();  // Qs ready (first pass) / previous block consumed
     load_latent_block(Cs, RS, R4, p.cache, p.cache_dtype, pt, p.page, j0, nkeys, R);
     __syncthreads();
@@ -127,7 +135,8 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
       s0 = fmaf(qv.x, a.x, s0); s0 = fmaf(qv.y, a.y, s0); s0 = fmaf(qv.z, a.z, s0); s0 = fmaf(qv.w, a.w, s0);
       s1 = fmaf(qv.x, b.x, s1); s1 = fmaf(qv.y, b.y, s1); s1 = fmaf(qv.z, b.z, s1); s1 = fmaf(qv.w, b.w, s1);
     }
-    const bool v0 = i < n && j0 + l <= my_last, v1 = i < n && j0 + l + 16 <= my_last;
+    const bool v0 = i < n && j0 + l <= my_last && j0 + l >= my_first;
+    const bool v1 = i < n && j0 + l + 16 <= my_last && j0 + l + 16 >= my_first;
     s0 = v0 ? s0 : kNegBig;
     s1 = v1 ? s1 : kNegBig;
     float bm = fmaxf(s0, s1);
@@ -228,8 +237,9 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   float m = has_sink ? p.sink[h] : kNegBig;   // meaningful in warp 0 only
   float lsum = has_sink ? 1.0f : 0.0f;
   const int nkeys = pos0 + 1;
+  const int first = p.window > 0 ? max(pos0 - p.window + 1, 0) : 0;   // sliding window: the first visible key
   const int jj_s = tid >> 3, sub = tid & 7;
-  for (int j0 = split * BKEY; j0 < nkeys; j0 += nsplit * BKEY) {
+  for (int j0 = (first / BKEY + split) * BKEY; j0 < nkeys; j0 += nsplit * BKEY) {
     __syncthreads();
     load_latent_block(Cs, RS, R4, p.cache, p.cache_dtype, pt, p.page, j0, nkeys, R);
     __syncthreads();
@@ -244,7 +254,7 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
     }
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (sub == 0) Ps[jj_s] = j0 + jj_s < nkeys ? s : kNegBig;
+    if (sub == 0) Ps[jj_s] = (j0 + jj_s < nkeys && j0 + jj_s >= first) ? s : kNegBig;
     __syncthreads();
     if (tid < 32) {
       const float sc = Ps[tid];
@@ -427,6 +437,54 @@ __global__ void __launch_bounds__(kThreads) sink_attn_tile_kernel(const vila_sin
   }
 }
 
+// One CTA per token.  Warp 0: RMS norm of the first R columns of the token's kv row -> pool row, all warps: the
+// rotary part of the kv row -> pool row columns R.., and the rotary part of every query head -> qa columns R..
+// of that head.  Angles in double, everything else fp32.
+__global__ void __launch_bounds__(kThreads) latent_rope_kernel(const vila_latent_rope_params p) {
+  extern __shared__ float cs[];   // cos [rot / 2] | sin [rot / 2]
+  const int t = blockIdx.x, tid = threadIdx.x, half = p.rot >> 1, RW = p.R + p.rot;
+  const double pos = static_cast<double>(p.positions[t]);
+  const float mag = p.mscale != 0.f ? p.mscale : 1.0f;
+  for (int i = tid; i < half; i += kThreads) {
+    double s, c;
+    sincos(pos * p.inv_freq[i], &s, &c);
+    cs[i] = static_cast<float>(c) * mag;
+    cs[half + i] = static_cast<float>(s) * mag;
+  }
+  __syncthreads();
+  const bool halves = p.layout == 1;
+  // rotated value of column c (0 .. rot - 1) of the vector that starts at element `base` of src
+  auto turned = [&](const void* src, int dt, size_t base, int c) {
+    const int o = halves ? (c < half ? c + half : c - half) : (c ^ 1);
+    const int i = halves ? (c < half ? c : c - half) : (c >> 1);
+    const bool second = halves ? c >= half : (c & 1) != 0;
+    const float v = ld_any(src, dt, base + c), w = ld_any(src, dt, base + o);
+    return second ? fmaf(v, cs[i], w * cs[half + i]) : fmaf(v, cs[i], -(w * cs[half + i]));
+  };
+  if (p.kv != nullptr) {
+    const size_t src = static_cast<size_t>(t) * p.ld_kv, dst = static_cast<size_t>(p.cache_rows[t]) * RW;
+    if (tid < 32) {
+      float ss = 0.f;
+      for (int c = tid; c < p.R; c += 32) {
+        const float v = ld_any(p.kv, p.kv_dtype, src + c);
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      const float r = 1.0f / sqrtf(ss / static_cast<float>(p.R) + p.eps);
+      for (int c = tid; c < p.R; c += 32)
+        st_any(p.pool, p.pool_dtype, dst + c, ld_any(p.kv, p.kv_dtype, src + c) * r * (p.norm_w ? p.norm_w[c] : 1.0f));
+    }
+    for (int c = tid; c < p.rot; c += kThreads) st_any(p.pool, p.pool_dtype, dst + p.R + c, turned(p.kv, p.kv_dtype, src + p.R, c));
+  }
+  if (p.q != nullptr) {
+    for (int idx = tid; idx < p.H * p.rot; idx += kThreads) {
+      const int h = idx / p.rot, c = idx - h * p.rot;
+      p.qa[(static_cast<size_t>(t) * p.H + h) * RW + p.R + c] =
+          turned(p.q, p.q_dtype, static_cast<size_t>(t) * p.ld_q + static_cast<size_t>(h) * p.q_head + p.q_off, c);
+    }
+  }
+}
+
 // dst[i] = src[rows[i]]: one warp per row, 16-byte pieces when everything is 16-byte aligned
 __global__ void __launch_bounds__(kThreads) gather_rows_kernel(const unsigned char* __restrict__ src,
                                                                const int32_t* __restrict__ rows,
@@ -456,7 +514,8 @@ int set_smem(K kern, size_t bytes) {
 int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   if (p.ntiles <= 0) return 0;
   VB_CHECK(p.R >= 1 && p.R <= 512, "latent_attention: latent width %d not in [1, 512]", p.R);
-  VB_CHECK(p.H >= 1 && p.H <= 65535 && p.page >= 1, "latent_attention: H=%d page=%d", p.H, p.page);
+  VB_CHECK(p.H >= 1 && p.H <= 65535 && p.page >= 1 && p.window >= 0, "latent_attention: H=%d page=%d window=%d", p.H,
+           p.page, p.window);
   const dim3 grid(p.ntiles, p.H), block(kThreads);
   if (p.decode && p.H >= 4) {
     // decoded tokens, several heads: the heads of a token are the rows of a tile (one latent load for all)
@@ -509,6 +568,18 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   else if (p.R <= 256) VB_LAT_TILE(4);
   else VB_LAT_TILE(8);
 #undef VB_LAT_TILE
+  return 0;
+}
+
+int latent_rope_append(const vila_latent_rope_params& p, cudaStream_t stream) {
+  if (p.T <= 0) return 0;
+  VB_CHECK(p.R >= 1 && p.rot >= 0 && p.rot % 2 == 0 && (p.rot == 0 || p.inv_freq != nullptr) && p.positions != nullptr &&
+               (p.layout == 0 || p.layout == 1),
+           "latent_rope_append: R=%d rot=%d layout=%d", p.R, p.rot, p.layout);
+  VB_CHECK(p.kv == nullptr || (p.pool != nullptr && p.cache_rows != nullptr), "latent_rope_append: kv rows need a pool");
+  VB_CHECK(p.q == nullptr || (p.qa != nullptr && p.H >= 1 && p.q_off >= 0 && p.q_off + p.rot <= p.q_head),
+           "latent_rope_append: H=%d q_head=%d q_off=%d rot=%d", p.H, p.q_head, p.q_off, p.rot);
+  VB_CUDA(launch_serial(latent_rope_kernel, dim3(p.T), dim3(kThreads), sizeof(float) * (p.rot + 2), stream, p));
   return 0;
 }
 

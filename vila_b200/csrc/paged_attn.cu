@@ -1,8 +1,9 @@
 // Grouped-query attention over a paged K/V pool for ragged batches, with the pieces a parallel-sublayer
 // decoder adds to it:
 //   rope_append_kernel   rotary positions on the first rot_dims columns of every q / k head (pairs
-//                        (2i, 2i+1), angle = position * inv_freq[i], evaluated in double so that far
-//                        positions keep their phase), optional unit norm per head (fp32), q out as fp32,
+//                        (2i, 2i+1) or (i, i + rot_dims / 2), angle = position * inv_freq[i], evaluated in
+//                        double so that far positions keep their phase; cos and sin optionally scaled by
+//                        one magnitude), optional unit norm per head (fp32), q out as fp32,
 //                        k | v appended to the pool row of the token
 //   paged_attn_kernel    fp32 scores of ALL H heads of a (query, key) pair, optional head mixing
 //                        s_h <- sum_g talk[h, g] s_g before the softmax, online softmax whose running
@@ -15,6 +16,13 @@
 // query and key (dist_bias [dist_rows, H], the last row serves every larger distance; added after scale and
 // mixing), a chunked mask (a query sees the keys of its own block of `chunk` positions only; the key loop
 // starts at the block of the tile's first row), and a per-(token, head) sigmoid gate on the output.
+// A sliding window with kept first tokens (a key is seen if it is at most window - 1 positions back, or among the
+// first keep_first of its sequence) is a mask plus a shorter block list: the blocks that hold kept tokens, then
+// the blocks from the window of the tile's first row on.  A per-head multiplier of the scores is folded into the
+// staged queries.  talk_after mixes the heads' softmax WEIGHTS: that needs every head's final (max, sum) before
+// any value is added, so the kernels first run over the key blocks with the scores only (pass 0), then again with
+// weights exp(s - max) / sum, mixed over heads, times the values (pass 1; nothing is rescaled).  When the keys of
+// a decoded token are dealt to several CTAs, each of them makes pass 0 over all blocks and pass 1 over its share.
 // Every reduction over keys runs in key order inside a block and block by block, so a row's result does
 // not depend on what else is in the launch.
 #include "../../include/vila_b200.h"
@@ -42,13 +50,19 @@ __global__ void __launch_bounds__(kThreads) rope_append_kernel(const vila_rope_a
   const int t = blockIdx.x, half = p.rot_dims >> 1;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const double pos = static_cast<double>(p.positions[t]);
+  const float mag = p.rot_mscale != 0.f ? p.rot_mscale : 1.0f;
   for (int i = tid; i < half; i += kThreads) {
     double s, c;
     sincos(pos * p.inv_freq[i], &s, &c);
-    cs[i] = static_cast<float>(c);
-    cs[half + i] = static_cast<float>(s);
+    cs[i] = static_cast<float>(c) * mag;
+    cs[half + i] = static_cast<float>(s) * mag;
   }
   __syncthreads();
+  // column c of the rotated part: its partner, its pair index and whether it is the second of its pair
+  const bool halves = p.rot_layout == 1;
+  auto partner = [&](int c) { return halves ? (c < half ? c + half : c - half) : (c ^ 1); };
+  auto pair_of = [&](int c) { return halves ? (c < half ? c : c - half) : (c >> 1); };
+  auto second = [&](int c) { return halves ? c >= half : (c & 1) != 0; };
   const size_t in0 = static_cast<size_t>(t) * p.ldq;
   const size_t prow = static_cast<size_t>(p.cache_rows[t]) * (static_cast<size_t>(p.G) * (p.dim + p.vdim));
   for (int hh = warp; hh < p.H + p.G; hh += kWarps) {
@@ -59,9 +73,9 @@ __global__ void __launch_bounds__(kThreads) rope_append_kernel(const vila_rope_a
     for (int c = lane; c < p.dim; c += 32) {
       float v = ld_any(p.qkv, p.qkv_dtype, src + c);
       if (c < p.rot_dims) {
-        const float o = ld_any(p.qkv, p.qkv_dtype, src + (c ^ 1));
-        const float co = cs[c >> 1], si = cs[half + (c >> 1)];
-        v = (c & 1) ? fmaf(v, co, o * si) : fmaf(v, co, -(o * si));
+        const float o = ld_any(p.qkv, p.qkv_dtype, src + partner(c));
+        const float co = cs[pair_of(c)], si = cs[half + pair_of(c)];
+        v = second(c) ? fmaf(v, co, o * si) : fmaf(v, co, -(o * si));
       }
       ss = fmaf(v, v, ss);
     }
@@ -73,9 +87,9 @@ __global__ void __launch_bounds__(kThreads) rope_append_kernel(const vila_rope_a
       if (p.v_from_k && !is_q)   // the value is the key as it came in
         st_any(p.pool, p.pool_dtype, prow + static_cast<size_t>(p.G) * p.dim + static_cast<size_t>(hh - p.H) * p.dim + c, v);
       if (c < p.rot_dims) {
-        const float o = ld_any(p.qkv, p.qkv_dtype, src + (c ^ 1));
-        const float co = cs[c >> 1], si = cs[half + (c >> 1)];
-        v = (c & 1) ? fmaf(v, co, o * si) : fmaf(v, co, -(o * si));
+        const float o = ld_any(p.qkv, p.qkv_dtype, src + partner(c));
+        const float co = cs[pair_of(c)], si = cs[half + pair_of(c)];
+        v = second(c) ? fmaf(v, co, o * si) : fmaf(v, co, -(o * si));
       }
       v *= r;
       if (nw) v *= nw[c];
@@ -106,6 +120,31 @@ __device__ __forceinline__ size_t pool_row(const int32_t* pt, int page, int j) {
 __device__ __forceinline__ int first_key(const vila_paged_attn_params& p, int pos) {
   return p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0;
 }
+// may the query at position pos see key j?
+__device__ __forceinline__ bool sees(const vila_paged_attn_params& p, int pos, int j) {
+  return j <= pos && j >= first_key(p, pos) && (p.window <= 0 || pos - j < p.window || j < p.keep_first);
+}
+// Key blocks of BK keys a tile visits, in order: [0, kb) then [wb, nblocks).
+struct BlockList {
+  int kb, wb, count;
+  __device__ __forceinline__ int block(int v) const { return v < kb ? v : wb + (v - kb); }
+};
+__device__ __forceinline__ BlockList visible_blocks(const vila_paged_attn_params& p, int pos0, int nkeys, int BK) {
+  BlockList b;
+  const int nblocks = (nkeys + BK - 1) / BK;
+  if (p.window <= 0) {
+    b.kb = 0;
+    b.wb = first_key(p, pos0) / BK;
+  } else {
+    b.kb = min((min(p.keep_first, nkeys) + BK - 1) / BK, nblocks);
+    b.wb = max(b.kb, max(max(pos0 - p.window + 1, 0), first_key(p, pos0)) / BK);
+  }
+  b.count = b.kb + max(nblocks - b.wb, 0);
+  return b;
+}
+__device__ __forceinline__ float head_scale(const vila_paged_attn_params& p, int h) {
+  return p.head_scale ? p.scale * p.head_scale[h] : p.scale;
+}
 __device__ __forceinline__ float dist_bias(const vila_paged_attn_params& p, int dist, int h) {
   return __ldg(p.dist_bias + static_cast<size_t>(min(dist, p.dist_rows - 1)) * p.H + h);
 }
@@ -118,7 +157,7 @@ __device__ __forceinline__ float out_gate(const vila_paged_attn_params& p, int r
 // g0, G: the K/V heads g0 .. g0 + G - 1 of the pool row are loaded (all of them by default).
 __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_paged_attn_params& p,
                                               const int32_t* pt, int j0, int nkeys, int BK, int D4, int DS, int V4,
-                                              int nwarps = kWarps, int g0 = 0, int G = 0) {
+                                              int nwarps = kWarps, int g0 = 0, int G = 0, bool with_v = true) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (G == 0) G = p.G;
   const int D = p.dim, V = p.vdim, KS = key_stride(G, DS);
@@ -149,7 +188,7 @@ __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_p
         *reinterpret_cast<float4*>(d + 4) = make_float4(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xffff0000u),
                                                         __uint_as_float(u.w << 16), __uint_as_float(u.w & 0xffff0000u));
       }
-      for (int x = lane; x < (G * V) >> 3; x += 32) {
+      for (int x = lane; with_v && x < (G * V) >> 3; x += 32) {
         const uint4 u = __ldg(v4 + x);
         float* d = vd + (x << 3);
         *reinterpret_cast<float4*>(d) = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
@@ -165,14 +204,14 @@ __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_p
         const int e = x << 2, g = e / D, k = e - g * D;
         *reinterpret_cast<float4*>(kd + g * DS + k) = __ldg(k4 + x);
       }
-      for (int x = lane; x < (G * V) >> 2; x += 32) *reinterpret_cast<float4*>(vd + (x << 2)) = __ldg(v4 + x);
+      for (int x = lane; with_v && x < (G * V) >> 2; x += 32) *reinterpret_cast<float4*>(vd + (x << 2)) = __ldg(v4 + x);
     } else {
       for (int x = lane; x < G * D4; x += 32) {
         const int g = x / D4, k = x - g * D4;
         kd[g * DS + k] = k < D ? ld_any(p.pool, p.pool_dtype, src + koff + static_cast<size_t>(g) * D + k) : 0.f;
       }
       const size_t vsrc = src + voff;
-      for (int x = lane; x < G * V4; x += 32) {
+      for (int x = lane; with_v && x < G * V4; x += 32) {
         const int g = x / V4, k = x - g * V4;
         vd[x] = k < V ? ld_any(p.pool, p.pool_dtype, vsrc + static_cast<size_t>(g) * V + k) : 0.f;
       }
@@ -209,11 +248,12 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
 
   for (int idx = tid; idx < R * D4; idx += kThreads) {
     const int r = idx / D4, k = idx - r * D4, i = r / H, h = r - i * H;
-    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * H + h) * D + k] * p.scale : 0.f;
+    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * H + h) * D + k] * head_scale(p, h) : 0.f;
   }
   for (int idx = tid; idx < H * H; idx += kThreads) Tk[idx] = p.talk ? p.talk[idx] : ((idx / H) == (idx % H) ? 1.f : 0.f);
+  const bool after = p.talk_after != 0 && p.talk != nullptr;
   for (int r = tid; r < R; r += kThreads) {
-    const bool first = split == 0 && p.sink != nullptr;
+    const bool first = split == 0 && p.sink != nullptr && !after;
     m_s[r] = first ? p.sink[r % H] : kNegBig;
     l_s[r] = first ? 1.0f : 0.0f;
   }
@@ -223,13 +263,18 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
   const int vq = V4 >> 2;                 // float4 columns of a head
   const int nout = R * vq;                // float4 accumulators of the CTA: index o -> (r, c4)
   const int nkeys = pos0 + n;             // keys 0 .. nkeys - 1 are visible to the last row
-  const int nblocks = (nkeys + BK - 1) / BK;
-  const int b0 = first_key(p, pos0) / BK;   // the first row's chunk starts first
+  const BlockList bl = visible_blocks(p, pos0, nkeys, BK);
 
-  for (int b = b0 + split; b < nblocks; b += nsplit) {
-    const int j0 = b * BK;
+  for (int pass = after ? 0 : 1; pass < 2; ++pass) {
+  const bool stats = pass == 0;   // scores only: every head's running max and sum over ALL visible keys
+  if (after && !stats) {
     __syncthreads();
-    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4);
+    for (int r = tid; r < R; r += kThreads) l_s[r] = l_s[r] > 0.f ? 1.0f / l_s[r] : 0.f;
+  }
+  for (int vb_ = stats ? 0 : split; vb_ < bl.count; vb_ += stats ? 1 : nsplit) {
+    const int j0 = bl.block(vb_) * BK;
+    __syncthreads();
+    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, kWarps, 0, 0, !stats);
     __syncthreads();
     // raw scores of every (score row, key)
     for (int idx = tid; idx < R * BK; idx += kThreads) {
@@ -245,10 +290,45 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
       Ss[idx] = s;
     }
     __syncthreads();
+    if (after) {
+      if (stats) {
+        // every head's own scores: running max and sum, nothing else
+        for (int r = warp; r < R; r += kWarps) {
+          const int i = r / H;
+          const bool valid = lane < BK && i < n && sees(p, pos0 + i, j0 + lane);
+          const float s = valid ? Ss[r * BK + lane] : kNegBig;
+          const float m_old = m_s[r];
+          const float m_new = fmaxf(m_old, warp_max(s));
+          const float ps = warp_sum(valid ? expf(s - m_new) : 0.f);
+          if (lane == 0) {
+            l_s[r] = l_s[r] * expf(m_old - m_new) + ps;
+            m_s[r] = m_new;
+          }
+        }
+        continue;
+      }
+      // final weights of every head (l_s holds 1 / sum), then their mix over heads; no rescaling of the sums
+      for (int idx = tid; idx < R * BK; idx += kThreads) {
+        const int r = idx / BK, jj = idx - r * BK, i = r / H;
+        Ss[idx] = (i < n && sees(p, pos0 + i, j0 + jj)) ? expf(Ss[idx] - m_s[r]) * l_s[r] : 0.f;
+      }
+      __syncthreads();
+      for (int r = warp; r < R; r += kWarps) {
+        const int i = r / H, h = r - i * H;
+        if (lane < BK) {
+          const float* tk = Tk + h * H;
+          const float* sr = Ss + (i * H) * BK + lane;
+          float w = 0.f;
+          for (int g = 0; g < H; ++g) w = fmaf(tk[g], sr[g * BK], w);
+          Ps[r * BK + lane] = w;
+        }
+        if (lane == 0) a_s[r] = 1.0f;
+      }
+    } else
     // head mixing + mask + online softmax: a warp per score row, a lane per key
     for (int r = warp; r < R; r += kWarps) {
       const int i = r / H, h = r - i * H;
-      const bool valid = lane < BK && i < n && j0 + lane <= pos0 + i && j0 + lane >= first_key(p, pos0 + i);
+      const bool valid = lane < BK && i < n && sees(p, pos0 + i, j0 + lane);
       float s = 0.f;
       if (lane < BK) {
         const float* tk = Tk + h * H;
@@ -290,6 +370,7 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
       }
     }
   }
+  }
   __syncthreads();
 #pragma unroll
   for (int a = 0; a < NACC; ++a) {
@@ -299,7 +380,7 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
     if (i >= n) continue;
     const float v[4] = {acc[a].x, acc[a].y, acc[a].z, acc[a].w};
     if (nsplit == 1) {
-      const float inv = out_gate(p, row0 + i, h) / l_s[r];
+      const float inv = after ? out_gate(p, row0 + i, h) : out_gate(p, row0 + i, h) / l_s[r];
       const size_t ob = (static_cast<size_t>(row0 + i) * H + h) * V + 4 * c4;
 #pragma unroll
       for (int e = 0; e < 4; ++e)
@@ -349,12 +430,14 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
 
   for (int idx = tid; idx < R * D4; idx += NT) {
     const int r = idx / D4, k = idx - r * D4, h = r / BQ, i = r - h * BQ;
-    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * p.H + h0 + h) * D + k] * p.scale : 0.f;
+    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * p.H + h0 + h) * D + k] * head_scale(p, h0 + h) : 0.f;
   }
   for (int idx = tid; idx < H * H; idx += NT) Tk[idx] = p.talk ? p.talk[idx] : ((idx / H) == (idx % H) ? 1.f : 0.f);
+  const bool after = p.talk_after != 0 && p.talk != nullptr;
   for (int r = tid; r < R; r += NT) {
-    m_s[r] = p.sink ? p.sink[h0 + r / BQ] : kNegBig;
-    l_s[r] = p.sink ? 1.0f : 0.0f;
+    const bool sink = p.sink != nullptr && !after;
+    m_s[r] = sink ? p.sink[h0 + r / BQ] : kNegBig;
+    l_s[r] = sink ? 1.0f : 0.0f;
   }
   float4 acc[NACC][4];
 #pragma unroll
@@ -366,9 +449,17 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
   const int nkeys = pos0 + n;
   const int d4n = D4 >> 2;
 
-  for (int j0 = (first_key(p, pos0) / BK) * BK; j0 < nkeys; j0 += BK) {
+  const BlockList bl = visible_blocks(p, pos0, nkeys, BK);
+  for (int pass = after ? 0 : 1; pass < 2; ++pass) {
+  const bool stats = pass == 0;   // scores only: every head's running max and sum over all visible keys
+  if (after && !stats) {
     __syncthreads();
-    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, NT / 32, g0, G);
+    for (int r = tid; r < R; r += NT) l_s[r] = l_s[r] > 0.f ? 1.0f / l_s[r] : 0.f;
+  }
+  for (int vb_ = 0; vb_ < bl.count; ++vb_) {
+    const int j0 = bl.block(vb_) * BK;
+    __syncthreads();
+    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, NT / 32, g0, G, !stats);
     __syncthreads();
     for (int item = tid; item < (R / TR) * HK; item += NT) {
       const int rbs = item / HK, jp = item - rbs * HK, r0 = rbs * TR;     // TR score rows of one head x 2 keys
@@ -398,6 +489,39 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
       }
     }
     __syncthreads();
+    if (after) {
+      if (stats) {
+        for (int r = warp; r < R; r += NT / 32) {
+          const int i = r % BQ;
+          const bool valid = lane < BK && i < n && sees(p, pos0 + i, j0 + lane);
+          const float s = valid ? Ss[r * BK + lane] : kNegBig;
+          const float m_old = m_s[r];
+          const float m_new = fmaxf(m_old, warp_max(s));
+          const float ps = warp_sum(valid ? expf(s - m_new) : 0.f);
+          if (lane == 0) {
+            l_s[r] = l_s[r] * expf(m_old - m_new) + ps;
+            m_s[r] = m_new;
+          }
+        }
+        continue;
+      }
+      for (int idx = tid; idx < R * BK; idx += NT) {
+        const int r = idx / BK, jj = idx - r * BK, i = r % BQ;
+        Ss[idx] = (i < n && sees(p, pos0 + i, j0 + jj)) ? expf(Ss[idx] - m_s[r]) * l_s[r] : 0.f;
+      }
+      __syncthreads();
+      for (int r = warp; r < R; r += NT / 32) {
+        const int h = r / BQ, i = r - h * BQ;
+        if (lane < BK) {
+          const float* tk = Tk + h * H;
+          const float* sr = Ss + i * BK + lane;
+          float w = 0.f;
+          for (int g = 0; g < H; ++g) w = fmaf(tk[g], sr[g * BQ * BK], w);
+          Ps[(((r >> 2) * BK + lane) << 2) + (r & 3)] = w;
+        }
+        if (lane == 0) a_s[r] = 1.0f;
+      }
+    } else
     // head mixing + mask + online softmax: a warp takes 4 score rows at a time (rows warp, warp + 8, ...), a
     // lane per key; the 4 rows' reductions are interleaved so that their shuffles overlap
     for (int rbase = warp; rbase < R; rbase += 4 * (NT / 32)) {
@@ -411,7 +535,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
         mo[u] = kNegBig;
         if (r < R) {
           const int h = r / BQ, i = r - h * BQ;
-          ok[u] = lane < BK && i < n && j0 + lane <= pos0 + i && j0 + lane >= first_key(p, pos0 + i);
+          ok[u] = lane < BK && i < n && sees(p, pos0 + i, j0 + lane);
           if (lane < BK) {
             const float* tk = Tk + h * H;
             const float* sr = Ss + i * BK + lane;
@@ -486,6 +610,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
       }
     }
   }
+  }
   __syncthreads();
 #pragma unroll
   for (int a = 0; a < NACC; ++a) {
@@ -496,7 +621,7 @@ __global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_a
     for (int k = 0; k < 4; ++k) {
       const int r = (rb << 2) + k, h = r / BQ, i = r - h * BQ;
       if (i >= n) continue;
-      const float inv = out_gate(p, row0 + i, h0 + h) / l_s[r];
+      const float inv = after ? out_gate(p, row0 + i, h0 + h) : out_gate(p, row0 + i, h0 + h) / l_s[r];
       const float v[4] = {acc[a][k].x, acc[a][k].y, acc[a][k].z, acc[a][k].w};
       const size_t ob = (static_cast<size_t>(row0 + i) * p.H + h0 + h) * V + 4 * c4;
 #pragma unroll
@@ -512,6 +637,15 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const vila_paged_
   const int row = tile[0], h = blockIdx.y, V = p.vdim, ns = p.nsplit;
   const float* part = p.partial + (static_cast<size_t>(row) * ns * p.H + h) * (V + 2);
   const size_t stride = static_cast<size_t>(p.H) * (V + 2);
+  if (p.talk_after != 0 && p.talk != nullptr) {   // the partial sums carry final weights: add them in split order
+    const float gt = out_gate(p, row, h);
+    for (int k = threadIdx.x; k < V; k += blockDim.x) {
+      float a = 0.f;
+      for (int s = 0; s < ns; ++s) a += part[s * stride + k];
+      st_any(p.out, p.out_dtype, (static_cast<size_t>(row) * p.H + h) * V + k, a * gt);
+    }
+    return;
+  }
   float mx = kNegBig;
   for (int s = 0; s < ns; ++s) mx = fmaxf(mx, part[s * stride + V]);
   float den = 0.f;
@@ -536,7 +670,8 @@ size_t attn_smem(const vila_paged_attn_params& p, int BQ, int BK, int H = 0, int
 int rope_append(const vila_rope_append_params& p, cudaStream_t stream) {
   if (p.T <= 0) return 0;
   VB_CHECK(p.H >= 1 && p.G >= 1 && p.dim >= 1 && p.vdim >= 1 && p.rot_dims >= 0 && p.rot_dims <= p.dim &&
-               p.rot_dims % 2 == 0 && (p.rot_dims == 0 || p.inv_freq != nullptr) && (!p.v_from_k || p.vdim == p.dim),
+               p.rot_dims % 2 == 0 && (p.rot_dims == 0 || p.inv_freq != nullptr) && (!p.v_from_k || p.vdim == p.dim) &&
+               (p.rot_layout == 0 || p.rot_layout == 1),
            "rope_append: H=%d G=%d dim=%d vdim=%d rot_dims=%d v_from_k=%d", p.H, p.G, p.dim, p.vdim, p.rot_dims,
            p.v_from_k);
   VB_CUDA(launch_serial(rope_append_kernel, dim3(p.T), dim3(kThreads), sizeof(float) * (p.rot_dims + 2), stream, p));
@@ -551,6 +686,8 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
   constexpr size_t kSmemMax = 224 * 1024;
   VB_CHECK(p.chunk >= 0 && (p.dist_bias == nullptr || p.dist_rows >= 1), "paged_attention: chunk=%d dist_rows=%d",
            p.chunk, p.dist_rows);
+  VB_CHECK(p.window >= 0 && p.keep_first >= 0 && (p.talk_after == 0 || (p.talk != nullptr && p.sink == nullptr)),
+           "paged_attention: window=%d keep_first=%d; talk_after needs talk and no sink", p.window, p.keep_first);
   VB_CHECK(p.max_rows >= 1 && p.max_rows <= 16 && (p.nsplit == 1 || p.max_rows == 1),
            "paged_attention: max_rows=%d nsplit=%d (key splitting serves one-row tiles)", p.max_rows, p.nsplit);
   AttnShape sh;

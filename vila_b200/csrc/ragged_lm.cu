@@ -74,6 +74,32 @@ rmsnorm_rows_kernel(const void* __restrict__ x, int x_dt, int64_t ldx, const voi
   }
 }
 
+// Pre-norm residual step in one pass: x += a + sum_j part_j (a first, then the partials by index), then
+// out = x / sqrt(mean(x^2) + eps) * w: the operand of the sublayer that reads x next.
+template <int TPR>
+__global__ void __launch_bounds__(kRowThreads)
+residual_norm_rows_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dt, int64_t lda,
+                          const void* __restrict__ part, int p_dt, int64_t ldp, int np, const void* __restrict__ w,
+                          int w_dt, float eps, void* __restrict__ out, int o_dt, int rows, int cols) {
+  __shared__ float red[kRowsPerCta];
+  const int row = row_of<TPR>();
+  if (row >= rows) return;
+  float* xr = x + static_cast<size_t>(row) * cols;
+  float ss = 0.f;
+  for (int c = col0_of<TPR>(); c < cols; c += TPR) {
+    float y = a ? ld_any(a, a_dt, static_cast<size_t>(row) * lda + c) : 0.f;
+    if (part)
+      for (int j = 0; j < np; ++j) y += ld_any(part, p_dt, (static_cast<size_t>(row) * np + j) * ldp + c);
+    const float v = xr[c] + y;
+    xr[c] = v;
+    ss += v * v;
+  }
+  ss = row_sum<TPR>(ss, red);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+  for (int c = col0_of<TPR>(); c < cols; c += TPR)   // every thread re-reads the columns it wrote itself
+    st_any(out, o_dt, static_cast<size_t>(row) * cols + c, xr[c] * r * (w ? ld_any(w, w_dt, c) : 1.0f));
+}
+
 __device__ __forceinline__ float gated_value(const void* part, int p_dt, int64_t ldp, int np,
                                              const void* gate, int g_dt, int64_t ldg,
                                              const void* gb, int b_dt, int row, int c) {
@@ -437,6 +463,19 @@ int rmsnorm_rows(const void* x, int x_dt, int64_t ldx, const void* w, int w_dt, 
   else
     VB_CUDA(launch_serial(rmsnorm_rows_kernel<32>, dim3(row_grid(vrows)), dim3(kRowThreads), 0, stream, x, x_dt,
                        ldx, w, w_dt, w_off, eps, out, o_dt, ldo, out_rows, vrows, vcols, groups));
+  return 0;
+}
+
+int residual_norm_rows(float* x, const void* a, int a_dt, int64_t lda, const void* part, int p_dt, int64_t ldp, int np,
+                       const void* w, int w_dt, float eps, void* out, int o_dt, int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  VB_CHECK(cols > 0 && out != nullptr && (part == nullptr || np >= 1), "residual_norm_rows: cols=%d n_partials=%d", cols, np);
+  if (cols >= kWideCols)
+    VB_CUDA(launch_serial(residual_norm_rows_kernel<256>, dim3(rows), dim3(kRowThreads), 0, stream, x, a, a_dt, lda,
+                          part, p_dt, ldp, np, w, w_dt, eps, out, o_dt, rows, cols));
+  else
+    VB_CUDA(launch_serial(residual_norm_rows_kernel<32>, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x, a,
+                          a_dt, lda, part, p_dt, ldp, np, w, w_dt, eps, out, o_dt, rows, cols));
   return 0;
 }
 

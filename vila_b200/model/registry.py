@@ -8,12 +8,13 @@ from typing import Dict, Optional
 
 import torch
 
+from .ludazen import LudazenForCausalLM
 from .lufatar import LufatarForCausalLM
 from .moronex import MoronexForCausalLM
 from .nusovik import NusovikForCausalLM
 
 LANGUAGE_MODELS: Dict[str, type] = {"Moronex": MoronexForCausalLM, "Lufatar": LufatarForCausalLM,
-                                    "Nusovik": NusovikForCausalLM}
+                                    "Nusovik": NusovikForCausalLM, "Ludazen": LudazenForCausalLM}
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 

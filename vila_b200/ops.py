@@ -48,9 +48,11 @@ def ensure_workspace(device, nbytes: int = 96 << 20) -> torch.Tensor:
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
            act: int = ACT_NONE, residual: Optional[torch.Tensor] = None, res_row_mod: int = 0,
            swiglu: bool = False, out: Optional[torch.Tensor] = None,
-           block_n: Optional[int] = None, static_w: bool = False) -> torch.Tensor:
+           block_n: Optional[int] = None, static_w: bool = False,
+           act_params: Optional[Tuple[float, float]] = None) -> torch.Tensor:
     """out = epilogue(x @ w.T).  x [M,K] (row stride arbitrary), w [N,K].
-    static_w: w is a parameter (VILA_FLAG_STATIC_W): it may be fetched before the PDL wait."""
+    static_w: w is a parameter (VILA_FLAG_STATIC_W): it may be fetched before the PDL wait.
+    act_params: the two coefficients of ACT_XIELU (positive side, negative side)."""
     _chk(x, "x"); _chk(w, "w")
     assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], (x.shape, w.shape)
     assert x.stride(1) == 1 and w.stride(1) == 1
@@ -71,7 +73,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     lib = _lib.load()
     args = (_p(x), x.stride(0), _p(w), w.stride(0), _p(bias), _p(residual), ld_res, res_row_mod,
             _p(out), out.stride(0), M, N, K, act, (1 if swiglu else 0) | (2 if static_w else 0), _stream())
-    if block_n is None:
+    if act_params is not None:
+        assert residual is None and block_n is None
+        check(lib.vila_linear_act(_p(x), x.stride(0), _p(w), w.stride(0), _p(bias), _p(out), out.stride(0), M, N, K,
+                                  act, float(act_params[0]), float(act_params[1]),
+                                  (1 if swiglu else 0) | (2 if static_w else 0), _stream()), "vila_linear_act")
+    elif block_n is None:
         check(lib.vila_linear(*args), "vila_linear")
     else:
         check(lib.vila_linear_cfg(block_n, *args), "vila_linear_cfg")
@@ -396,6 +403,7 @@ def decode_attention_batch(qkv: torch.Tensor, positions: torch.Tensor, k_pool: t
 # ---- ragged-batch language-model blocks (fp32 residual stream) -------------------------------------
 DT_BF16, DT_F32 = 0, 1
 ACT_RELU2 = 4
+ACT_XIELU = 5   # z > 0: a_pos z^2 + z / 2;  z <= 0: a_neg (e^z - 1 - z) + z / 2  (act_params = (a_pos, a_neg))
 _DT = {torch.bfloat16: DT_BF16, torch.float32: DT_F32}
 
 
@@ -477,11 +485,14 @@ def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
             groups: int = 1, a_group_off: int = 0, o_group_off: int = 0,
             seg: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None, a_row_div: int = 1,
             o_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
-            out_rows_total: Optional[int] = None, glu_clamp: Optional[Tuple[float, float]] = None) -> torch.Tensor:
+            out_rows_total: Optional[int] = None, glu_clamp: Optional[Tuple[float, float]] = None,
+            act_params: Optional[Tuple[float, float]] = None, in_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Any-shape (grouped) linear layer, fp32 accumulation on the CUDA cores (vila_glinear).
     w [N, K] (groups == 1) or [groups, N, K].  Batched groups (seg None): group g reads the A columns
     [g * a_group_off, + K) and writes the output columns [g * o_group_off, + N).  Segmented (seg int32
-    [groups + 1]): the rows of group g are the sorted positions seg[g]..seg[g+1]; see the header."""
+    [groups + 1]): the rows of group g are the sorted positions seg[g]..seg[g+1]; see the header.
+    act_params: the coefficients of ACT_XIELU.  in_scale fp32: sorted position i is computed from its input row
+    times in_scale[a_rows[i]] (a_rows None: in_scale[i]): the scale enters before bias and activation."""
     assert a.dim() == 2 and a.stride(1) == 1
     if w.dim() == 2:
         w = w[None]
@@ -509,8 +520,11 @@ def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
     p.M, p.N, p.K, p.groups = M, N, K, groups
     p.mode = 0 if seg is None else 1
     p.a_row_div, p.act, p.flags = a_row_div, act, (1 if swiglu else 0) | (4 if glu_clamp is not None else 0)
-    if glu_clamp is not None:
-        ext = _lib.GLinearExt(float(glu_clamp[0]), float(glu_clamp[1]))
+    if glu_clamp is not None or act_params is not None or in_scale is not None:
+        assert in_scale is None or o_rows is None
+        ext = _lib.GLinearExt(float(glu_clamp[0]) if glu_clamp else 1.0, float(glu_clamp[1]) if glu_clamp else float("inf"),
+                              float(act_params[0]) if act_params else 0.0, float(act_params[1]) if act_params else 0.0,
+                              _f32(in_scale, "in_scale"))
         check(_lib.load().vila_glinear_x(C.byref(p), C.byref(ext), _stream()), "vila_glinear_x")
     else:
         check(_lib.load().vila_glinear(C.byref(p), _stream()), "vila_glinear")
@@ -520,10 +534,11 @@ def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_tables: torch.Tensor, tiles: torch.Tensor,
                      *, heads: int, page: int, scale: float, sink: Optional[torch.Tensor] = None,
                      gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype=None,
-                     decode: bool = False, nsplit: int = 1) -> torch.Tensor:
+                     decode: bool = False, nsplit: int = 1, window: int = 0) -> torch.Tensor:
     """q fp32 [T, heads * R] (key expansion already folded in), cache [pool rows, R], page_tables int32
     [slots, max_pages], tiles int32 [ntiles, 4] (row0, rows, pos0, slot) -> [T, heads * R].
-    decode: one-row tiles; nsplit > 1 spreads the keys of every row over nsplit CTAs + a merge kernel."""
+    decode: one-row tiles; nsplit > 1 spreads the keys of every row over nsplit CTAs + a merge kernel.
+    window > 0: a row sees itself and the window - 1 tokens before it only."""
     assert q.dtype == torch.float32 and q.is_contiguous() and q.dim() == 2
     assert cache.dim() == 2 and cache.is_contiguous()
     R = cache.shape[1]
@@ -542,12 +557,41 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_tables: torch.Te
     p.ntiles, p.pt_stride = tiles.shape[0], page_tables.stride(0)
     p.H, p.R, p.page, p.decode, p.scale = heads, R, page, 1 if decode else 0, scale
     p.nsplit = max(1, int(nsplit)) if decode else 1
+    p.window = int(window)
     partial = None
     if p.nsplit > 1:
         partial = torch.empty(q.shape[0] * heads * p.nsplit * (R + 2), dtype=torch.float32, device=q.device)
         p.partial = partial.data_ptr()
     check(_lib.load().vila_latent_attention(C.byref(p), _stream()), "vila_latent_attention")
     return out
+
+
+def latent_rope_append(positions: torch.Tensor, inv_freq: torch.Tensor, *, rank: int, layout: int = 0,
+                       mscale: float = 1.0, kv: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+                       eps: float = 1e-6, pool: Optional[torch.Tensor] = None,
+                       cache_rows: Optional[torch.Tensor] = None, q: Optional[torch.Tensor] = None,
+                       qa: Optional[torch.Tensor] = None, heads: int = 0, q_head: int = 0, q_off: int = 0) -> None:
+    """Cache rows and query parts of latent attention with a decoupled rotary part (rot = 2 * inv_freq.numel()).
+    kv [T, >= rank + rot]: pool row cache_rows[t] = rmsnorm(kv[t, :rank]) * norm_w | rotate(kv[t, rank : rank + rot]).
+    q [T, >= heads * q_head]: qa[t, h, rank : rank + rot] = rotate(q[t, h * q_head + q_off : + rot]) (qa fp32
+    [T, heads * (rank + rot)], its other columns are left alone).  layout 0: pairs (2i, 2i + 1), 1: (i, i + rot / 2)."""
+    assert inv_freq.dtype == torch.float64 and inv_freq.is_cuda and inv_freq.is_contiguous()
+    rot = 2 * inv_freq.numel()
+    p = _lib.LatentRopeParams()
+    p.positions, p.inv_freq = _i32(positions, "positions"), _p(inv_freq)
+    p.T, p.R, p.rot, p.layout, p.eps, p.mscale = positions.numel(), rank, rot, layout, eps, mscale
+    if kv is not None:
+        assert kv.dim() == 2 and kv.stride(1) == 1 and kv.shape[1] >= rank + rot and kv.shape[0] == p.T
+        assert pool.dim() == 2 and pool.is_contiguous() and pool.shape[1] == rank + rot
+        p.kv, p.ld_kv, p.kv_dtype = _p(kv), kv.stride(0), _dt(kv, "kv")
+        p.norm_w, p.pool, p.pool_dtype = _f32(norm_w, "norm_w"), _p(pool), _dt(pool, "pool")
+        p.cache_rows = _i32(cache_rows, "cache_rows")
+    if q is not None:
+        assert q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= heads * q_head and q.shape[0] == p.T
+        assert qa.dtype == torch.float32 and qa.is_contiguous() and qa.shape == (p.T, heads * (rank + rot))
+        p.q, p.ld_q, p.q_dtype, p.qa = _p(q), q.stride(0), _dt(q, "q"), _p(qa)
+        p.H, p.q_head, p.q_off = heads, q_head, q_off
+    check(_lib.load().vila_latent_rope_append(C.byref(p), _stream()), "vila_latent_rope_append")
 
 
 def hgrn2_scan(proj: torch.Tensor, state: torch.Tensor, seqs: torch.Tensor, *, heads: int, dim: int, vdim: int,
@@ -627,15 +671,16 @@ def sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tiles: tor
 
 # ---- parallel-sublayer decoders: pair embedding, short convolution, rotary GQA over a paged pool, sigmoid router ----
 def linear_any(x: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out_dtype=None,
-               bias: Optional[torch.Tensor] = None, act: int = ACT_NONE) -> torch.Tensor:
+               bias: Optional[torch.Tensor] = None, act: int = ACT_NONE,
+               act_params: Optional[Tuple[float, float]] = None) -> torch.Tensor:
     """act(x [M, K] · w[N, K]^T + bias): bf16 operands with 16-byte aligned rows go to the tcgen05 GEMM,
     everything else (fp32 tensors, odd shapes, an fp32 result) to the CUDA-core grouped kernel."""
     N, K = w.shape
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16)
             and K % 8 == 0 and N % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and (not swiglu or N % 32 == 0)):
-        return linear(x, w, bias, act=act, swiglu=swiglu, static_w=True)
-    return glinear(x, w, swiglu=swiglu, out_dtype=out_dtype, bias=bias, act=act)
+        return linear(x, w, bias, act=act, swiglu=swiglu, static_w=True, act_params=act_params)
+    return glinear(x, w, swiglu=swiglu, out_dtype=out_dtype, bias=bias, act=act, act_params=act_params)
 
 
 def embed_pair_rows(table: torch.Tensor, pair_table: torch.Tensor, ids: torch.Tensor, prev_ids: torch.Tensor,
@@ -713,11 +758,14 @@ def norm_conv_rows(x: torch.Tensor, norm_w: Sequence[torch.Tensor], conv_w: Sequ
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Tensor, pool: torch.Tensor, *,
                 heads: int, kv_heads: int, dim: int, vdim: int, inv_freq: Optional[torch.Tensor],
                 unit_norm: bool, eps: float, q_norm_w: Optional[torch.Tensor] = None,
-                k_norm_w: Optional[torch.Tensor] = None, v_from_k: bool = False) -> torch.Tensor:
+                k_norm_w: Optional[torch.Tensor] = None, v_from_k: bool = False, halves: bool = False,
+                mscale: float = 1.0) -> torch.Tensor:
     """qkv [T, >= heads*dim + kv_heads*(dim+vdim)] -> q fp32 [T, heads*dim] (rotated, unit-normed); the
     token's k | v go to row cache_rows[t] of pool [pool rows, kv_heads*(dim+vdim)].  inv_freq float64
     [rot_dims / 2] (None: no rotation).  q_norm_w / k_norm_w fp32 [dim]: weights of the per-head norm.
-    v_from_k: qkv holds q | k only, the cached value of a token is its incoming key (before rotation / norm)."""
+    v_from_k: qkv holds q | k only, the cached value of a token is its incoming key (before rotation / norm).
+    halves: column i of the rotated part pairs with i + rot_dims / 2 instead of 2i with 2i + 1; mscale multiplies
+    cos and sin (a magnitude correction of rescaled frequencies)."""
     assert qkv.dim() == 2 and qkv.stride(1) == 1
     assert qkv.shape[1] >= heads * dim + kv_heads * (dim if v_from_k else dim + vdim)
     assert not v_from_k or vdim == dim
@@ -738,6 +786,7 @@ def rope_append(qkv: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Te
     for t_ in (q_norm_w, k_norm_w):
         assert t_ is None or (unit_norm and t_.numel() == dim)
     p.q_norm_w, p.k_norm_w, p.v_from_k = _f32(q_norm_w, "q_norm_w"), _f32(k_norm_w, "k_norm_w"), 1 if v_from_k else 0
+    p.rot_layout, p.rot_mscale = 1 if halves else 0, float(mscale)
     check(_lib.load().vila_rope_append(C.byref(p), _stream()), "vila_rope_append")
     return q
 
@@ -747,14 +796,18 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, page_tables: torch.Tens
                     talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
                     out: Optional[torch.Tensor] = None, out_dtype=None, max_rows: int = 16,
                     nsplit: int = 1, dist_bias: Optional[torch.Tensor] = None, chunk: int = 0,
-                    gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    gate: Optional[torch.Tensor] = None, window: int = 0, keep_first: int = 0,
+                    talk_after: bool = False, head_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal grouped-query attention of q fp32 [T, heads*dim] over the paged k | v pool, fp32 scores and
     softmax, optional mixing of the heads' scores (talk fp32 [heads, heads]) and per-head sink logit in
     the denominator.  tiles int32 [n, 4] = (row0, rows <= max_rows, pos0, slot) -> [T, heads*vdim].
     nsplit > 1 (one-row tiles only) spreads the keys of a row over nsplit CTAs + a merge kernel.
     dist_bias fp32 [rows, heads]: added to the score by distance (the last row for every larger one);
     chunk > 0: a query sees its own block of `chunk` positions only; gate [T, >= heads] (a view with a
-    row stride is fine): the output of head h is multiplied by sigmoid(gate[t, h])."""
+    row stride is fine): the output of head h is multiplied by sigmoid(gate[t, h]).
+    window > 0: a key is seen only when it is less than `window` positions back or among the first `keep_first`
+    of its sequence.  talk_after: talk mixes the heads' softmax weights instead of their scores (no sink then).
+    head_scale fp32 [heads]: per-head multiplier of the scores."""
     assert q.dtype == torch.float32 and q.is_contiguous() and q.shape[1] == heads * dim
     assert pool.dim() == 2 and pool.is_contiguous() and pool.shape[1] == kv_heads * (dim + vdim)
     if out is None:
@@ -777,6 +830,10 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, page_tables: torch.Tens
         assert gate.dim() == 2 and gate.shape[0] == q.shape[0] and gate.shape[1] >= heads and gate.stride(1) == 1
         p.gate, p.ldg, p.gate_dtype = _p(gate), gate.stride(0), _dt(gate, "gate")
     p.chunk = int(chunk)
+    p.window, p.keep_first, p.talk_after = int(window), int(keep_first), 1 if talk_after else 0
+    if head_scale is not None:
+        assert head_scale.numel() == heads
+        p.head_scale = _f32(head_scale, "head_scale")
     p.nsplit = max(1, int(nsplit)) if max_rows == 1 else 1
     partial = None
     if p.nsplit > 1:
@@ -819,6 +876,25 @@ def residual_add_rows(x: torch.Tensor, a: Optional[torch.Tensor] = None, part: O
         n_partials, mult, _p(copy), _dt(copy, "copy") if copy is not None else 0, rows, cols, _stream()),
         "vila_residual_add_rows")
     return copy
+
+
+def residual_norm_rows(x: torch.Tensor, a: Optional[torch.Tensor], w: Optional[torch.Tensor], eps: float, *,
+                       part: Optional[torch.Tensor] = None, n_partials: int = 1, out_dtype=None) -> torch.Tensor:
+    """x fp32 [rows, cols] (in place) += a[r] + sum_j part[r * n_partials + j]; -> rmsnorm(x) * w in out_dtype (the
+    operand of the sublayer that reads x next): the residual sum and the following pre-norm in one pass."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    rows, cols = x.shape
+    if a is not None:
+        assert a.shape == (rows, cols) and a.stride(1) == 1
+    if part is not None:
+        assert part.shape == (rows * n_partials, cols) and part.stride(1) == 1
+    out = torch.empty(rows, cols, dtype=out_dtype or x.dtype, device=x.device)
+    check(_lib.load().vila_residual_norm_rows(
+        _p(x), _p(a), _dt(a, "a") if a is not None else 0, a.stride(0) if a is not None else 0,
+        _p(part), _dt(part, "part") if part is not None else 0, part.stride(0) if part is not None else 0,
+        n_partials, _p(w), _dt(w, "w") if w is not None else 0, eps, _p(out), _dt(out, "out"), rows, cols, _stream()),
+        "vila_residual_norm_rows")
+    return out
 
 
 def gelu_mul_gather(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int, *, out_dtype=None) -> torch.Tensor:
