@@ -3,6 +3,7 @@ from .configuration import (LlavaConfig, Qwen2Config, SiglipVisionConfig, nvila_
                             nvila_8b_dynamic_s2, nvila_lite_3b, nvila_video_8b, tiny_test_config)
 from .llava_llama import (BasicImageEncoder, BasicVideoEncoder, LlavaLlamaModel, SyntheticTokenizer,
                           TSPVideoEncoder)
+from .ludazen import LudazenConfig, LudazenForCausalLM, LudazenLayerConfig
 from .lufatar import LufatarConfig, LufatarForCausalLM, LufatarLayerConfig
 from .modeling_vila import VILAForCausalLM
 from .moronex import MoronexConfig, MoronexForCausalLM, MoronexLayerConfig

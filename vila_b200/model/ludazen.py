@@ -183,8 +183,8 @@ class LudazenConfig:
         out = []
         for lc in self.layers:
             if lc.type == "attention":
-                m = {"dim": lc.dim, "heads": lc.heads, "kv_heads": lc.kv_heads,
-                     "mask": {"keep_first": lc.keep_first, "size": lc.window}, "rot": lc.rot.to_dict(),
+                mask = {"keep_first": lc.keep_first, "size": lc.window} if lc.keep_first else {"size": lc.window}
+                m = {"dim": lc.dim, "heads": lc.heads, "kv_heads": lc.kv_heads, "mask": mask, "rot": lc.rot.to_dict(),
                      "scale": lc.scale, "vdim": lc.vdim}
             else:
                 m = {"dim": lc.dim, "heads": lc.heads, "kv_rank": lc.kv_rank, "mask": {"size": lc.window},
