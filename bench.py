@@ -1624,6 +1624,228 @@ def run_ssm_lm(args):
 
 
 
+# ------------------------------------------------------------------------------------------------
+# --workload window_lm: the Ludazen windowed-attention language model next to Lufatar (the closest model of
+# the package: same engine, rotary grouped-query attention over a paged k | v pool with head mixing, sigmoid
+# router, gated experts) at equal width / heads / vocabulary / experts, random weights, bf16.  The latent
+# layers are set beside Moronex's latent-attention kernel in the ledger.
+# ------------------------------------------------------------------------------------------------
+WINDOW_LM = dict(window=1024, keep_first=64, kv_rank=384, rot_dim=64)
+
+
+def window_lm_config(z):
+    H, G, W = z["heads"], z["kv_heads"], z["width"]
+    att = dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5,
+               rot={"base": 10000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+               mask={"size": WINDOW_LM["window"], "keep_first": WINDOW_LM["keep_first"]})
+    lat = dict(heads=H, dim=128, rot_dim=WINDOW_LM["rot_dim"], vdim=128, kv_rank=WINDOW_LM["kv_rank"], scale=192 ** -0.5,
+               rot={"base": 10000.0, "dims": WINDOW_LM["rot_dim"]}, mask={"size": WINDOW_LM["window"]})
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["expert_ff"]}}
+    dense = {"kind": "dense", "ff": 4 * W}
+    layers = [{"type": "attention", "mixer": dict(att), "mlp": dict(dense)}, {"type": "attention", "mixer": dict(att), "mlp": dict(moe)},
+              {"type": "latent_attention", "mixer": dict(lat), "mlp": dict(dense)},
+              {"type": "latent_attention", "mixer": dict(lat, kv_from=2), "mlp": dict(moe)}]
+    return {"architecture": "Ludazen", "layers": layers, "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": W}
+
+
+def window_lm_block(args, peaks):
+    import torch
+
+    from vila_b200 import ops
+    from vila_b200.model import LudazenConfig, LudazenForCausalLM, LufatarConfig, LufatarForCausalLM
+    from vila_b200.serving import TokenEngine
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=args.steps, warm=max(3, args.warmup), setup=None):
+        ts = []
+        for i in range(warm + reps):
+            if setup is not None:
+                setup()
+            flush.fill_(i & 255)     # evict L2 (126 MB) between iterations
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    def timed_op(fn):
+        """a single op of the kernel ledger: captured once, timed as a graph replay, so that the number is
+        the device time of its launches and not the host time of the Python call around them"""
+        fn()
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return timed(g.replay)
+
+    S, B, CTX, NEW = 2048, 8, 1024, 32
+    tf, gbs = peaks["bf16_tflops"], peaks["hbm_gbs"]
+    bf = torch.bfloat16
+    out = {}
+    t00 = time.time()
+
+    def log(msg):
+        print("[window_lm %6.1fs] %s" % (time.time() - t00, msg), file=sys.stderr, flush=True)
+
+    def engine_numbers(lm, prompt):
+        eng = TokenEngine(lm, max_tokens=B * (CTX + 4 * NEW + 64), slots=B)
+        t_pre = timed(lambda: eng.step([("p", prompt, [S - 1])]), setup=lambda: eng.release("p"))
+        eng.release("p")
+        for b in range(B):
+            eng.step([(b, prompt[:CTX], [])])
+        step_in = [[(b, [int(prompt[(k * 7 + b) % S])], [0]) for b in range(B)] for k in range(NEW)]
+
+        def decode_run():
+            for k in range(NEW):
+                eng.step(step_in[k])
+        t_dec = timed(decode_run, reps=3, warm=1)     # contexts grow CTX .. CTX + 4 * NEW: fits the reserve
+        for b in range(B):
+            eng.release(b)
+        n = sum(v.numel() for v in lm.weights.values())
+        return eng, {"params_m": n / 1e6, "prefill_tok_s": S / t_pre * 1e3, "prefill_ms": t_pre,
+                     "decode_tok_s": B * NEW / t_dec * 1e3, "decode_ms_per_step": t_dec / NEW}
+
+    def flops(t, fl):
+        return {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+
+    def bytes_(t, by):
+        return {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+
+    win, keep, R, Dr = WINDOW_LM["window"], WINDOW_LM["keep_first"], WINDOW_LM["kv_rank"], WINDOW_LM["rot_dim"]
+    RW = R + Dr
+    for name, z in PARALLEL_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        W, H, G = z["width"], z["heads"], z["kv_heads"]
+        g = torch.Generator().manual_seed(0)
+        prompt = torch.randint(0, z["vocab"], (S,), generator=g).tolist()
+        log("size %s: ludazen" % name)
+        lm = LudazenForCausalLM(LudazenConfig.from_dict(window_lm_config(z)), dev, bf).init_random(0, on_device=True)
+        eng, res_new = engine_numbers(lm, prompt)
+        log("size %s: lufatar" % name)
+        tw = LufatarForCausalLM(LufatarConfig.from_dict(parallel_lm_config(z)), dev, bf).init_random(0, on_device=True)
+        eng2, res_old = engine_numbers(tw, prompt)
+        # ---- kernel beside the like kernel ---------------------------------------------------------------
+        log("kernel ledger")
+        led = {}
+        La, Lm, Ll, T0 = lm.layers[0], lm.layers[1], lm.layers[2], tw.layers[0]
+        page, npg = eng.cache.page, eng.cache.n_pages
+        pool = eng.cache.latent[0]
+        pt = torch.arange(npg, dtype=torch.int32, device=dev).view(1, -1).repeat(B, 1).contiguous()
+        tiles = torch.tensor([(o, 16, o, 0) for o in range(0, S, 16)], dtype=torch.int32, device=dev)
+        q = torch.randn(S, H * 128, device=dev)
+        # (query, key) pairs a mask lets through
+        pairs_win = sum(min(p + 1, win) + max(0, min(keep, p + 1 - win)) for p in range(S))
+        pairs_all = S * (S + 1) // 2
+        wkw = dict(heads=H, kv_heads=G, dim=128, vdim=128, page=page, scale=0.088, talk=La.talk, talk_after=True,
+                   head_scale=La.temp, window=win, keep_first=keep)
+        t = timed_op(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, **wkw))
+        led["paged_attention prefill: window %d + %d kept, weights mixed after the softmax (two passes over the keys)" % (win, keep)] = \
+            flops(t, H * pairs_win * 4.0 * 128)
+        okw = dict(heads=H, kv_heads=G, dim=128, vdim=128, page=page, scale=0.088, talk=T0.talk, sink=T0.sink)
+        t = timed_op(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, **okw))
+        led["lufatar paged_attention prefill: plain causal, scores mixed before the softmax"] = flops(t, H * pairs_all * 4.0 * 128)
+        t = timed_op(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, window=win, keep_first=keep, **okw))
+        led["paged_attention prefill: the same window, scores mixed before the softmax (one pass)"] = flops(t, H * pairs_win * 4.0 * 128)
+        dt_ = torch.tensor([(b, 1, CTX - 1, b) for b in range(B)], dtype=torch.int32, device=dev)
+        pt2 = ((torch.arange(B, device=dev, dtype=torch.int32)[:, None] * (CTX // page) +
+                torch.arange(npg, device=dev, dtype=torch.int32)[None]) % npg).contiguous()
+        ns = lm._splits(eng.cache, win + keep)
+        t = timed_op(lambda: ops.paged_attention(q[:B], pool, pt2, dt_, max_rows=1, nsplit=ns, **wkw))
+        led["paged_attention decode: window, weights mixed after the softmax (8 x 1024 keys, %d CTAs per row)" % ns] = \
+            bytes_(t, B * CTX * G * 256 * 2)
+        t = timed_op(lambda: ops.paged_attention(q[:B], pool, pt2, dt_, max_rows=1, nsplit=eng2.cache.decode_splits, **okw))
+        led["lufatar paged_attention decode (8 x 1024 keys, %d CTAs per row)" % eng2.cache.decode_splits] = bytes_(t, B * CTX * G * 256 * 2)
+        # latent attention over (latent | rotated key part) rows, beside the same kernel without window and rotary part
+        lpool = eng.cache.latent[2]
+        qa = torch.randn(S, H * RW, device=dev)
+        t = timed_op(lambda: ops.latent_attention(qa, lpool, pt, tiles, heads=H, page=page, scale=0.072, window=win))
+        led["latent_attention prefill: rows of %d + %d, window %d" % (R, Dr, win)] = flops(t, H * sum(min(p + 1, win) for p in range(S)) * 4.0 * RW)
+        t = timed_op(lambda: ops.latent_attention(qa, lpool, pt, tiles, heads=H, page=page, scale=0.072))
+        led["moronex-style latent_attention prefill: the same rows, plain causal"] = flops(t, H * pairs_all * 4.0 * RW)
+        ns = lm._splits(eng.cache, win)
+        t = timed_op(lambda: ops.latent_attention(qa[:B], lpool, pt2, dt_, heads=H, page=page, scale=0.072, window=win, decode=True, nsplit=ns))
+        led["latent_attention decode: window (8 x 1024 keys, %d CTAs per row)" % ns] = bytes_(t, B * CTX * RW * 2)
+        t = timed_op(lambda: ops.latent_attention(qa[:B], lpool, pt2, dt_, heads=H, page=page, scale=0.072, decode=True,
+                                                  nsplit=eng.cache.decode_splits))
+        led["moronex-style latent_attention decode: plain causal (8 x 1024 keys, %d CTAs per row)" % eng.cache.decode_splits] = \
+            bytes_(t, B * CTX * RW * 2)
+        ar = torch.arange(S, dtype=torch.int32, device=dev)
+        P = torch.randn(S, H * 192 + RW, device=dev).to(bf)
+        t = timed_op(lambda: ops.latent_rope_append(ar, Ll.inv_freq, rank=R, kv=P[:, H * 192:], norm_w=Ll.dkv_norm, eps=1e-5,
+                                                    pool=lpool, cache_rows=ar, q=P, qa=qa, heads=H, q_head=192, q_off=128))
+        led["latent_rope_append: latent norm + rotary key part -> cache row, rotary query parts (2048 rows)"] = \
+            bytes_(t, S * ((RW + H * Dr) * 2 + RW * 2 + H * Dr * 4))
+        qkv = torch.randn(S, (H + 2 * G) * 128, device=dev).to(bf)
+        t = timed_op(lambda: ops.rope_append(qkv, ar, ar, pool, heads=H, kv_heads=G, dim=128, vdim=128, inv_freq=La.inv_freq,
+                                             unit_norm=False, eps=1e-5, halves=True, mscale=La.magnitude))
+        by = S * ((H + 2 * G) * 128 * 2 + H * 128 * 4 + 2 * G * 128 * 2)
+        led["rope_append: rotary in halves, rescaled frequencies + k | v append (2048 rows)"] = bytes_(t, by)
+        t = timed_op(lambda: ops.rope_append(qkv, ar, ar, eng2.cache.latent[0], heads=H, kv_heads=G, dim=128, vdim=128,
+                                             inv_freq=T0.inv_freq, unit_norm=True, eps=1e-5))
+        led["lufatar rope_append: rotary in pairs + unit norm + k | v append (2048 rows)"] = bytes_(t, by)
+        # feed-forwards
+        h = torch.randn(S, W, device=dev).to(bf)
+        fl = 2 * 3 * S * z["top"] * z["expert_ff"] * W
+        t = timed_op(lambda: lm._experts(Lm, h))
+        led["routed + shared experts prefill: sigmoid router + group + 2 grouped GEMMs (weight on the input) + shared gated unit"] = \
+            flops(t, fl + 2 * 3 * S * z["expert_ff"] * W)
+        t = timed_op(lambda: tw._experts(T0, h))
+        led["lufatar routed experts prefill: group-limited sigmoid router + group + 2 grouped GEMMs"] = flops(t, fl)
+        t = timed_op(lambda: lm._experts(Lm, h[:B]))
+        by = 3 * min(z["experts"], B * z["top"]) * z["expert_ff"] * W * 2
+        led["routed + shared experts decode (8 rows)"] = bytes_(t, by + 3 * z["expert_ff"] * W * 2)
+        t = timed_op(lambda: tw._experts(T0, h[:B]))
+        led["lufatar routed experts decode (8 rows)"] = bytes_(t, by)
+        t = timed_op(lambda: ops.linear_any(h, La.up, bias=La.up_b, act=ops.ACT_XIELU, act_params=La.act))
+        led["dense feed-forward up-projection, bias + two-sided quadratic/exponential epilogue (tcgen05)"] = flops(t, 2.0 * S * W * 4 * W)
+        t = timed_op(lambda: ops.linear_any(h, La.up, bias=La.up_b, act=ops.ACT_RELU2))
+        led["the same projection with the squared-ReLU epilogue (tcgen05)"] = flops(t, 2.0 * S * W * 4 * W)
+        # residual stream
+        x = torch.randn(S, W, device=dev)
+        y = torch.randn(S, W, device=dev).to(bf)
+        parts = torch.randn(S * z["top"], W, device=dev)
+        t = timed_op(lambda: ops.residual_norm_rows(x, y, La.norm1, 1e-5, part=parts, n_partials=z["top"], out_dtype=bf))
+        led["residual_norm_rows: x += shared + expert partials, then the next pre-norm (2048 rows)"] = \
+            bytes_(t, S * W * (8 + 2 + 4 * z["top"] + 2))
+        t = timed_op(lambda: ops.residual_add_rows(x, y, parts, n_partials=z["top"], mult=0.5))
+        led["lufatar residual_add_rows: x += m (attention + expert partials) (2048 rows)"] = bytes_(t, S * W * (8 + 2 + 4 * z["top"]))
+        out[name] = {"ludazen": res_new, "lufatar": res_old, "kernels": led}
+        del lm, tw, eng, eng2
+        torch.cuda.empty_cache()
+    return {"workload": "window_lm: 4 Ludazen layers (windowed rotary GQA with weight mixing + dense / routed feed-forward, "
+                        "windowed latent attention with a rotary part + dense / routed feed-forward, the second latent layer "
+                        "on the first one's rows) vs 4 Lufatar layers (rotary GQA with score mixing + routed experts in "
+                        "parallel) of equal width / heads / vocabulary / experts; prefill: one %d-token prompt; decode: %d "
+                        "sequences x %d-token context, %d steps" % (S, B, CTX, NEW),
+            "dtype": "bf16", "data": "synthetic (random weights, random ids)",
+            "l2_policy": "256 MB buffer written between timed iterations",
+            "kernel_ledger_timing": "each op captured in a CUDA graph, one replay per timed iteration", "peaks": peaks, "sizes": out}
+
+
+def run_window_lm(args):
+    import torch
+    assert torch.cuda.is_available(), "bench.py --workload window_lm needs a GPU"
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("VILA_BENCH_WATCHDOG_S", "480")), exit=True)
+    peaks = read_peaks()
+    with ClockSampler(0) as cs:
+        res = window_lm_block(args, peaks)
+    res["clocks"] = cs.summary()
+    from vila_b200 import _lib
+    res["gpu_launches"] = _lib.LAUNCHES
+    print(json.dumps(res))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1638,11 +1860,12 @@ def main():
     ap.add_argument("--sp-steps", type=int, default=10)
     ap.add_argument("--profile", action="store_true",
                     help="profiling aid (ncu): 1 warm-up, 8 new tokens, no extra blocks; NOT a valid bench number")
-    ap.add_argument("--sizes", default="", help="hybrid_lm / parallel_lm / ssm_lm: comma-separated subset of the workload's sizes ("
+    ap.add_argument("--sizes", default="", help="hybrid_lm / parallel_lm / ssm_lm / window_lm: comma-separated subset of the workload's sizes ("
                     + ",".join(HYBRID_SIZES) + " / " + ",".join(PARALLEL_SIZES) + ")")
-    ap.add_argument("--workload", default="headline", choices=["headline", "hybrid_lm", "parallel_lm", "ssm_lm"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "hybrid_lm", "parallel_lm", "ssm_lm", "window_lm"],
                     help="headline (default): the NVILA-8B serving step; hybrid_lm: Moronex vs Qwen2 at equal size; "
-                         "parallel_lm: Lufatar vs Moronex at equal size; ssm_lm: Nusovik vs Moronex at equal size")
+                         "parallel_lm: Lufatar vs Moronex at equal size; ssm_lm: Nusovik vs Moronex at equal size; "
+                         "window_lm: Ludazen vs Lufatar at equal size")
     args = ap.parse_args()
     if args.workload == "hybrid_lm":
         return run_hybrid_lm(args)
@@ -1650,6 +1873,8 @@ def main():
         return run_parallel_lm(args)
     if args.workload == "ssm_lm":
         return run_ssm_lm(args)
+    if args.workload == "window_lm":
+        return run_window_lm(args)
     if args.profile:
         global NEW_TOKENS
         NEW_TOKENS = 8

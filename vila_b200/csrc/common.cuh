@@ -81,6 +81,12 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
 __device__ __forceinline__ float xielu_f(float z, float a_pos, float a_neg) {
   return z > 0.f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
 }
+// the same for epilogues whose result is rounded to bf16 right after: fast exponential, no branch
+__device__ __forceinline__ float xielu_fast_f(float z, float a_pos, float a_neg) {
+  const float zn = fminf(z, 0.f);
+  const float neg = a_neg * (__expf(zn) - 1.0f - zn), pos = a_pos * z * z;
+  return fmaf(0.5f, z, z > 0.f ? pos : neg);
+}
 __device__ __forceinline__ float gelu_erf_f(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
 }

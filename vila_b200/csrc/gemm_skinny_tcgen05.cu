@@ -461,7 +461,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                                 ? gelu_tanh_f(xb)
                                 : (act == ACT_GELU_ERF ? gelu_erf_f(xb)
                                                        : (act == ACT_RELU2 ? fmaxf(xb, 0.f) * fmaxf(xb, 0.f)
-                                                          : (act == ACT_XIELU ? xielu_f(xb, a.epi.act_pos, a.epi.act_neg) : silu_f(xb))));
+                                                          : (act == ACT_XIELU ? xielu_fast_f(xb, a.epi.act_pos, a.epi.act_neg) : silu_f(xb))));
             sts_bf16(dst + j * kStgPitch, y);
           }
         }

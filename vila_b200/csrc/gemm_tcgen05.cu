@@ -468,7 +468,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          ? gelu_tanh_f(x)
                          : (epi.act == ACT_GELU_ERF ? gelu_erf_f(x)
                                                     : (epi.act == ACT_RELU2 ? fmaxf(x, 0.f) * fmaxf(x, 0.f)
-                                                       : (epi.act == ACT_XIELU ? xielu_f(x, epi.act_pos, epi.act_neg) : silu_f(x))));
+                                                       : (epi.act == ACT_XIELU ? xielu_fast_f(x, epi.act_pos, epi.act_neg) : silu_f(x))));
             }
           }
           if (row_ok) {

@@ -22,7 +22,8 @@
 // staged queries.  talk_after mixes the heads' softmax WEIGHTS: that needs every head's final (max, sum) before
 // any value is added, so the kernels first run over the key blocks with the scores only (pass 0), then again with
 // weights exp(s - max) / sum, mixed over heads, times the values (pass 1; nothing is rescaled).  When the keys of
-// a decoded token are dealt to several CTAs, each of them makes pass 0 over all blocks and pass 1 over its share.
+// a decoded token are dealt to several CTAs, pass 0 and pass 1 are two launches: the first leaves every CTA's
+// (max, sum) of its share in the partial records, the second merges them in split order and adds its share.
 // Every reduction over keys runs in key order inside a block and block by block, so a row's result does
 // not depend on what else is in the launch.
 #include "../../include/vila_b200.h"
@@ -110,6 +111,9 @@ struct AttnShape {
   int sub;     // CTAs per 16-row tile (grid.y)
   int hsplit;  // head groups per tile (grid.z of the tiled kernel): 1 = all heads in one CTA, G = one K/V head and
                // its query heads per CTA (possible when the heads' scores are not mixed)
+  int phase;   // weights mixed after the softmax with the keys of a row dealt to several CTAs: 0 = this launch only
+               // leaves every CTA's running (max, sum) in its partial record, 1 = this launch merges those records and
+               // adds its share of the values; -1 = one CTA does both passes itself
 };
 
 __device__ __forceinline__ size_t pool_row(const int32_t* pt, int page, int j) {
@@ -265,13 +269,29 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
   const int nkeys = pos0 + n;             // keys 0 .. nkeys - 1 are visible to the last row
   const BlockList bl = visible_blocks(p, pos0, nkeys, BK);
 
-  for (int pass = after ? 0 : 1; pass < 2; ++pass) {
-  const bool stats = pass == 0;   // scores only: every head's running max and sum over ALL visible keys
+  const int pass_begin = after && sh.phase != 1 ? 0 : 1, pass_end = after && sh.phase == 0 ? 1 : 2;
+  for (int pass = pass_begin; pass < pass_end; ++pass) {
+  const bool stats = pass == 0;   // scores only: every head's running max and sum over the visible keys
   if (after && !stats) {
     __syncthreads();
-    for (int r = tid; r < R; r += kThreads) l_s[r] = l_s[r] > 0.f ? 1.0f / l_s[r] : 0.f;
+    for (int r = tid; r < R; r += kThreads) {
+      if (sh.phase == 1) {   // (max, sum) of every split's share, merged in split order
+        const int i = r / H, h = r - i * H;
+        float mx = kNegBig, l = 0.f;
+        if (i < n) {
+          const float* rec = p.partial + (static_cast<size_t>(row0 + i) * nsplit * H + h) * (V + 2) + V;
+          const size_t step = static_cast<size_t>(H) * (V + 2);
+          for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, rec[s * step]);
+          for (int s = 0; s < nsplit; ++s) l += expf(rec[s * step] - mx) * rec[s * step + 1];
+        }
+        m_s[r] = mx;
+        l_s[r] = l;
+      }
+      l_s[r] = l_s[r] > 0.f ? 1.0f / l_s[r] : 0.f;
+    }
   }
-  for (int vb_ = stats ? 0 : split; vb_ < bl.count; vb_ += stats ? 1 : nsplit) {
+  const bool all_blocks = stats && sh.phase < 0;
+  for (int vb_ = all_blocks ? 0 : split; vb_ < bl.count; vb_ += all_blocks ? 1 : nsplit) {
     const int j0 = bl.block(vb_) * BK;
     __syncthreads();
     load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, kWarps, 0, 0, !stats);
@@ -387,10 +407,13 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
         if (4 * c4 + e < V) st_any(p.out, p.out_dtype, ob + e, v[e] * inv);
     } else {
       float* part = p.partial + ((static_cast<size_t>(row0 + i) * nsplit + split) * H + h) * (V + 2);
+      if (!(after && sh.phase == 0)) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (4 * c4 + e < V) part[4 * c4 + e] = v[e];
-      if (c4 == 0) { part[V] = m_s[r]; part[V + 1] = l_s[r]; }
+        for (int e = 0; e < 4; ++e)
+          if (4 * c4 + e < V) part[4 * c4 + e] = v[e];
+      }
+      // with the weights mixed afterwards the (max, sum) slots belong to the first launch: the second one reads them
+      if (c4 == 0 && !(after && sh.phase == 1)) { part[V] = m_s[r]; part[V + 1] = l_s[r]; }
     }
   }
 }
@@ -691,6 +714,7 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
   VB_CHECK(p.max_rows >= 1 && p.max_rows <= 16 && (p.nsplit == 1 || p.max_rows == 1),
            "paged_attention: max_rows=%d nsplit=%d (key splitting serves one-row tiles)", p.max_rows, p.nsplit);
   AttnShape sh;
+  sh.phase = -1;
   // Without head mixing the K/V-head groups are independent: a CTA then serves ONE K/V head and its query heads, holds
   // a quarter .. an eighth of the K | V block, and takes more rows of the sequence instead.
   sh.hsplit = (p.talk == nullptr && p.max_rows > 1) ? p.G : 1;
@@ -748,11 +772,16 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
                                    static_cast<int>(smem)));                                                     \
     VB_CUDA(launch_serial(paged_attn_kernel<N>, grid, dim3(kThreads), smem, stream, p, sh));                     \
   } while (0)
-  if (nacc <= 1) VB_PAGED(1);
-  else if (nacc <= 2) VB_PAGED(2);
-  else if (nacc <= 4) VB_PAGED(4);
-  else if (nacc <= 8) VB_PAGED(8);
-  else VB_PAGED(16);
+  // weights mixed after the softmax + split keys: the (max, sum) launch, then the launch that adds the values
+  const int launches = (p.talk_after != 0 && p.nsplit > 1) ? 2 : 1;
+  for (int l = 0; l < launches; ++l) {
+    sh.phase = launches == 2 ? l : -1;
+    if (nacc <= 1) VB_PAGED(1);
+    else if (nacc <= 2) VB_PAGED(2);
+    else if (nacc <= 4) VB_PAGED(4);
+    else if (nacc <= 8) VB_PAGED(8);
+    else VB_PAGED(16);
+  }
 #undef VB_PAGED
   if (p.nsplit > 1)
     VB_CUDA(launch_serial(paged_attn_merge_kernel, dim3(p.ntiles, p.H), dim3(128), 0, stream, p));

@@ -399,8 +399,8 @@ class LudazenForCausalLM:
 
     @staticmethod
     def _splits(cache, visible: int) -> int:
-        """CTAs per decoded row: the pool's choice, but no more than one per 256 keys a window lets a row see"""
-        return max(1, min(cache.decode_splits, (visible + 255) // 256))
+        """CTAs per decoded row: the pool's choice, but no more than one per 64 keys a window lets a row see"""
+        return max(1, min(cache.decode_splits, (visible + 63) // 64))
 
     def _latent_attention(self, L: _Layer, h, batch, cache):
         lc, T = L.cfg, h.shape[0]
