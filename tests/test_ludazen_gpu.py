@@ -323,7 +323,8 @@ def test_window_edges_and_kept_tokens_show(cuda, decode):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF])
-@pytest.mark.parametrize("H,R,rot,size", [(3, 20, 6, 21), (1, 12, 4, 1000), (4, 64, 16, 33), (8, 64, 8, 128), (2, 9, 2, 1), (16, 40, 24, 64)])
+@pytest.mark.parametrize("H,R,rot,size", [(3, 20, 6, 21), (1, 12, 4, 1000), (4, 64, 16, 33), (8, 64, 8, 128), (2, 9, 2, 1), (16, 40, 24, 64),
+                                          (5, 560, 8, 70), (2, 530, 4, 40)])
 def test_latent_rows_and_windowed_latent_attention(cuda, dtype, H, R, rot, size):
     """cache rows (normed latent | rotated key part) and folded queries from latent_rope_append, then the windowed
     attention over them in tiles and as single rows with split keys, against separate keys and values in float64"""

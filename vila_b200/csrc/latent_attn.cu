@@ -513,7 +513,7 @@ int set_smem(K kern, size_t bytes) {
 
 int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   if (p.ntiles <= 0) return 0;
-  VB_CHECK(p.R >= 1 && p.R <= 512, "latent_attention: latent width %d not in [1, 512]", p.R);
+  VB_CHECK(p.R >= 1 && p.R <= 1024, "latent_attention: latent width %d not in [1, 1024]", p.R);
   VB_CHECK(p.H >= 1 && p.H <= 65535 && p.page >= 1 && p.window >= 0, "latent_attention: H=%d page=%d window=%d", p.H,
            p.page, p.window);
   const dim3 grid(p.ntiles, p.H), block(kThreads);
@@ -532,7 +532,8 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
     if (p.R <= 64) VB_LAT_HEADS(1);
     else if (p.R <= 128) VB_LAT_HEADS(2);
     else if (p.R <= 256) VB_LAT_HEADS(4);
-    else VB_LAT_HEADS(8);
+    else if (p.R <= 512) VB_LAT_HEADS(8);
+    else VB_LAT_HEADS(16);
 #undef VB_LAT_HEADS
     if (p.nsplit > 1)
       VB_CUDA(launch_serial(latent_attn_merge_kernel, dim3(p.ntiles, p.H), block, 0, stream, p));
@@ -549,9 +550,12 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
     if (p.R <= 256) {
       if (set_smem(latent_attn_decode_kernel<1>, smem)) return 2;
       VB_CUDA(launch_serial(latent_attn_decode_kernel<1>, dgrid, block, smem, stream, p, rp));
-    } else {
+    } else if (p.R <= 512) {
       if (set_smem(latent_attn_decode_kernel<2>, smem)) return 2;
       VB_CUDA(launch_serial(latent_attn_decode_kernel<2>, dgrid, block, smem, stream, p, rp));
+    } else {
+      if (set_smem(latent_attn_decode_kernel<4>, smem)) return 2;
+      VB_CUDA(launch_serial(latent_attn_decode_kernel<4>, dgrid, block, smem, stream, p, rp));
     }
     if (p.nsplit > 1) VB_CUDA(launch_serial(latent_attn_merge_kernel, grid, block, 0, stream, p));
     return 0;
@@ -566,7 +570,8 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   if (p.R <= 64) VB_LAT_TILE(1);
   else if (p.R <= 128) VB_LAT_TILE(2);
   else if (p.R <= 256) VB_LAT_TILE(4);
-  else VB_LAT_TILE(8);
+  else if (p.R <= 512) VB_LAT_TILE(8);
+  else VB_LAT_TILE(16);
 #undef VB_LAT_TILE
   return 0;
 }

@@ -566,17 +566,18 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_tables: torch.Te
     return out
 
 
-def latent_rope_append(positions: torch.Tensor, inv_freq: torch.Tensor, *, rank: int, layout: int = 0,
+def latent_rope_append(positions: torch.Tensor, inv_freq: Optional[torch.Tensor], *, rank: int, layout: int = 0,
                        mscale: float = 1.0, kv: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
                        eps: float = 1e-6, pool: Optional[torch.Tensor] = None,
                        cache_rows: Optional[torch.Tensor] = None, q: Optional[torch.Tensor] = None,
                        qa: Optional[torch.Tensor] = None, heads: int = 0, q_head: int = 0, q_off: int = 0) -> None:
-    """Cache rows and query parts of latent attention with a decoupled rotary part (rot = 2 * inv_freq.numel()).
+    """Cache rows and query parts of latent attention with a decoupled rotary part (rot = 2 * inv_freq.numel();
+    inv_freq None: no rotary part, only the normed latent is written).
     kv [T, >= rank + rot]: pool row cache_rows[t] = rmsnorm(kv[t, :rank]) * norm_w | rotate(kv[t, rank : rank + rot]).
     q [T, >= heads * q_head]: qa[t, h, rank : rank + rot] = rotate(q[t, h * q_head + q_off : + rot]) (qa fp32
     [T, heads * (rank + rot)], its other columns are left alone).  layout 0: pairs (2i, 2i + 1), 1: (i, i + rot / 2)."""
-    assert inv_freq.dtype == torch.float64 and inv_freq.is_cuda and inv_freq.is_contiguous()
-    rot = 2 * inv_freq.numel()
+    assert inv_freq is None or (inv_freq.dtype == torch.float64 and inv_freq.is_cuda and inv_freq.is_contiguous())
+    rot = 0 if inv_freq is None else 2 * inv_freq.numel()
     p = _lib.LatentRopeParams()
     p.positions, p.inv_freq = _i32(positions, "positions"), _p(inv_freq)
     p.T, p.R, p.rot, p.layout, p.eps, p.mscale = positions.numel(), rank, rot, layout, eps, mscale
