@@ -1636,7 +1636,7 @@ WINDOW_LM = dict(window=1024, keep_first=64, kv_rank=384, rot_dim=64)
 def window_lm_config(z):
     H, G, W = z["heads"], z["kv_heads"], z["width"]
     att = dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5,
-               rot={"base": 10000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+               rot={"base": 10000.0, "dims": 128, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}},
                mask={"size": WINDOW_LM["window"], "keep_first": WINDOW_LM["keep_first"]})
     lat = dict(heads=H, dim=128, rot_dim=WINDOW_LM["rot_dim"], vdim=128, kv_rank=WINDOW_LM["kv_rank"], scale=192 ** -0.5,
                rot={"base": 10000.0, "dims": WINDOW_LM["rot_dim"]}, mask={"size": WINDOW_LM["window"]})

@@ -192,7 +192,7 @@ def check_logits(cfg, model, prompts, got, dtype):
 # ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [F32, BF])
 @pytest.mark.parametrize("H,G,dim,vdim,rot,scaling", [(3, 3, 12, 20, 8, None), (4, 1, 10, 6, 10, (4.0, 64, 8.0, 2.0)),
-                                                      (2, 2, 16, 16, 0, None), (10, 2, 64, 32, 32, (8.0, 256, 32.0, 1.0))])
+                                                      (2, 2, 16, 16, 0, None), (10, 2, 64, 32, 32, (6.0, 256, 24.0, 1.5))])
 def test_rotation_in_halves_with_rescaled_frequencies(cuda, dtype, H, G, dim, vdim, rot, scaling):
     """positions near 0, at a page border and far; q comes back rotated (fp32), k | v land in the named pool rows"""
     from vila_b200.model.ludazen import RotaryConfig
